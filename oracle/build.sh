@@ -1,0 +1,36 @@
+#!/usr/bin/env bash
+# Builds the CPU oracle (test infrastructure) and, when a reference checkout is
+# available, the pieces of the reference that compile on their own:
+#   oracle/libamsim_oracle.so      C restatement (always)
+#   oracle/_ref/libref_amsim.so    reference cuda/AMsimulator.inl as host C++
+#   oracle/_ref/lut/*.bin          output of the reference's lut/lut_gen.cc
+#   oracle/_ref/lut/MBM_11.bin     m = 11 LUT from cuda/FPmultMBM_fast32.inl
+# Reference sources are compiled where they lie; nothing is copied.
+# Usage: oracle/build.sh [reference_dir]   (default /root/reference)
+set -euo pipefail
+here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+ref="${1:-${AMSIM_REFERENCE_DIR:-/root/reference}}"
+
+gcc -O2 -fPIC -shared -fopenmp -ffp-contract=off -fno-fast-math -std=c11 \
+    -o "$here/libamsim_oracle.so" "$here/amsim_oracle.c" -lm
+
+if [ -f "$ref/cuda/AMsimulator.inl" ]; then
+  mkdir -p "$here/_ref/lut"
+  g++ -O2 -fPIC -shared -std=c++14 -I"$ref/cuda" \
+      -o "$here/_ref/libref_amsim.so" "$here/ref_shim.cc"
+  # lut/lut_gen.cc writes <MODEL>_<m>.bin into the current directory
+  # (lut/lut_gen.cc:88-97); same compile line as lut/lut_gen.sh:14.
+  tmp="$(mktemp -d)"
+  for mul in FMBM16_MULTIPLIER FMBM14_MULTIPLIER FMBM12_MULTIPLIER FMBM10_MULTIPLIER \
+             MITCHEL16_MULTIPLIER MITCHEL14_MULTIPLIER MITCHEL12_MULTIPLIER \
+             MITCHEL10_MULTIPLIER BFLOAT; do
+    g++ -w -D$mul -I"$ref/lut" -o "$tmp/lut_gen_$mul" "$ref/lut/lut_gen.cc"
+    (cd "$here/_ref/lut" && "$tmp/lut_gen_$mul")
+  done
+  g++ -w -O1 -D__device__= -I"$ref/cuda" -o "$tmp/gen_lut_m11" "$here/gen_lut_m11.cc"
+  "$tmp/gen_lut_m11" "$here/_ref/lut/MBM_11.bin"
+  rm -rf "$tmp"
+  echo "oracle/_ref built from $ref"
+else
+  echo "no reference checkout at $ref: oracle/_ref not rebuilt"
+fi
