@@ -1,0 +1,586 @@
+// C ABI of the AM-Simulator kernels (declared in include/amsim.h): LUT handles,
+// argument checking, launch configuration.  Device code is in
+// amsim_kernels.cuh.  Nothing here synchronises the device or exits.
+#include "../../include/amsim.h"
+
+#include <cuda_runtime.h>
+#include <limits.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "amsim_kernels.cuh"
+
+using namespace amsim;
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                          \
+  do {                                                                                          \
+    cudaError_t e_ = (expr);                                                                    \
+    if (e_ != cudaSuccess) return fail(AMSIM_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+constexpr int kTargetCtas = 2 * 148;  // two resident CTAs on each of the 148 SMs
+
+}  // namespace
+
+struct amsim_lut {
+  int m = 0;
+  int device = 0;
+  int refs = 0;
+  std::string key;
+  uint8_t* d_raw = nullptr;    // 2^(2m) bytes as in the file
+  uint8_t* d_canon = nullptr;  // encoded, row = first operand (a)   [m <= 7]
+  uint8_t* d_trans = nullptr;  // encoded, row = second operand (b)  [m <= 7]
+  int enc_bytes = 0;           // size of each encoded copy, multiple of 16
+};
+
+namespace {
+
+std::mutex g_lut_mu;
+std::map<std::string, amsim_lut*> g_lut_cache;
+
+// approx_mul_lut.h:22-25
+int parse_mant_width(const char* path) {
+  const char* us = strrchr(path, '_');
+  const char* dot = strrchr(path, '.');
+  if (!us || !dot || dot <= us + 1) return -1;
+  int m = 0;
+  for (const char* p = us + 1; p < dot; ++p) {
+    if (*p < '0' || *p > '9') return -1;
+    m = m * 10 + (*p - '0');
+    if (m > 99) return -1;
+  }
+  return (m >= 1 && m <= 11) ? m : -1;
+}
+
+// Table byte as the kernels consume it: carry and mantissa merged into one
+// number so that  entry << (23 - m)  is exactly what AMsimulator.inl:22-23,31-32
+// add to the exponent/mantissa bits.
+inline uint8_t encode_entry(uint8_t v, int m) { return (uint8_t)(((v >> 7) << m) + (v & 0x7f)); }
+
+int upload_lut(const uint8_t* bytes, int m, int device, amsim_lut** out) {
+  int prev = 0;
+  CUDA_TRY(cudaGetDevice(&prev));
+  CUDA_TRY(cudaSetDevice(device));
+  amsim_lut* h = new amsim_lut();
+  h->m = m;
+  h->device = device;
+  h->refs = 1;
+  const size_t n = (size_t)1 << (2 * m);
+  int rc = AMSIM_OK;
+  auto bail = [&](cudaError_t e, const char* what) {
+    rc = fail(AMSIM_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  };
+  cudaError_t e = cudaMalloc(&h->d_raw, n);
+  if (e != cudaSuccess) bail(e, "cudaMalloc(lut)");
+  if (rc == AMSIM_OK) {
+    e = cudaMemcpy(h->d_raw, bytes, n, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) bail(e, "cudaMemcpy(lut)");
+  }
+  if (rc == AMSIM_OK && m <= 7) {
+    const int side = 1 << m, stride = side + 4;
+    h->enc_bytes = (side * stride + 15) / 16 * 16;
+    std::vector<uint8_t> canon(h->enc_bytes, 0), trans(h->enc_bytes, 0);
+    for (int a = 0; a < side; ++a)
+      for (int b = 0; b < side; ++b) {
+        const uint8_t v = encode_entry(bytes[a * side + b], m);
+        canon[a * stride + b] = v;
+        trans[b * stride + a] = v;
+      }
+    e = cudaMalloc(&h->d_canon, h->enc_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_trans, h->enc_bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(h->d_canon, canon.data(), h->enc_bytes, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(h->d_trans, trans.data(), h->enc_bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) bail(e, "upload of encoded lut");
+  }
+  cudaSetDevice(prev);
+  if (rc != AMSIM_OK) {
+    cudaFree(h->d_raw);
+    cudaFree(h->d_canon);
+    cudaFree(h->d_trans);
+    delete h;
+    return rc;
+  }
+  *out = h;
+  return AMSIM_OK;
+}
+
+int check_common(const amsim_lut* lut, unsigned flags, bool need_gemm) {
+  if (!lut) return fail(AMSIM_ERR_INVALID, "lut handle is NULL");
+  if (flags & ~AMSIM_DETERMINISTIC) return fail(AMSIM_ERR_INVALID, "unknown flag bits 0x%x", flags);
+  if (need_gemm && lut->m > 7)
+    return fail(AMSIM_ERR_UNSUPPORTED, "GEMM kernels hold the table in shared memory: m = %d > 7 is not supported", lut->m);
+  int dev = -1;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev != lut->device)
+    return fail(AMSIM_ERR_INVALID, "current device %d differs from the LUT's device %d", dev, lut->device);
+  return AMSIM_OK;
+}
+
+template <typename K>
+int ensure_smem(K kernel, size_t bytes, int device) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, size_t> done;
+  std::lock_guard<std::mutex> lk(mu);
+  auto key = std::make_pair((const void*)kernel, device);
+  auto it = done.find(key);
+  if (it != done.end() && it->second >= bytes) return AMSIM_OK;
+  CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  done[key] = bytes;
+  return AMSIM_OK;
+}
+
+void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
+  // The table row is selected by the warp-uniform operand U.  When the lane
+  // operand V is the multiplier's first operand (a), U is b: rows indexed by b.
+  p.lut = v_is_first_operand ? lut->d_trans : lut->d_canon;
+  p.lut_bytes = lut->enc_bytes;
+  p.m = lut->m;
+  p.mult = 1u << (23 - lut->m);
+  p.rowstride = (1u << lut->m) + 4u;
+}
+
+void fill_gather_divs(Gather& g) {
+  g.d_img = make_fastdiv((uint32_t)(g.PH * g.PW));
+  g.d_pw = make_fastdiv((uint32_t)g.PW);
+  g.d_sc = make_fastdiv((uint32_t)g.SC);
+  g.d_kw = make_fastdiv((uint32_t)g.KW);
+  g.d_dh = make_fastdiv((uint32_t)g.dil_h);
+  g.d_dw = make_fastdiv((uint32_t)g.dil_w);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <int WP, bool EXACT, bool VEC>
+int launch_gather_t(cudaStream_t st, const Params& p, int batch, int device) {
+  using L = SmemLayout<WP, EXACT>;
+  const size_t smem = L::bytes(p.lut_bytes);
+  int rc = ensure_smem(gather_gemm<WP, EXACT, VEC>, smem, device);
+  if (rc) return rc;
+  dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, batch);
+  gather_gemm<WP, EXACT, VEC><<<grid, L::NT, smem, st>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  return AMSIM_OK;
+}
+
+int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device) {
+  if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
+  if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");
+  const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
+  const long long ctas2 = (long long)((p.P + 255) / 256) * ((p.Q + BQ - 1) / BQ) * batch;
+  const bool wide = ctas2 >= 148;
+#define AMSIM_GO(WP_, EX_, VEC_) return launch_gather_t<WP_, EX_, VEC_>(st, p, batch, device)
+  if (wide) {
+    if (exact) { if (vec) AMSIM_GO(2, true, true); else AMSIM_GO(2, true, false); }
+    else       { if (vec) AMSIM_GO(2, false, true); else AMSIM_GO(2, false, false); }
+  } else {
+    if (exact) { if (vec) AMSIM_GO(1, true, true); else AMSIM_GO(1, true, false); }
+    else       { if (vec) AMSIM_GO(1, false, true); else AMSIM_GO(1, false, false); }
+  }
+#undef AMSIM_GO
+}
+
+struct FgradPlan {
+  int wp, splits, k_chunk;
+  size_t ws_bytes;
+};
+
+FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
+  FgradPlan f;
+  const double waste1 = (double)((P + 127) / 128) * 128 / (P > 0 ? P : 1);
+  const double waste2 = (double)((P + 255) / 256) * 256 / (P > 0 ? P : 1);
+  f.wp = (waste2 <= waste1 + 0.02) ? 2 : 1;
+  const int bp = f.wp * 128;
+  const long long tiles = (long long)((P + bp - 1) / bp) * ((Q + BQ - 1) / BQ);
+  int splits = 1;
+  if (!exact && tiles > 0) {
+    splits = (int)((kTargetCtas + tiles - 1) / tiles);
+    const int max_splits = (K + 4 * BK - 1) / (4 * BK);  // at least 4 stages per split
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+  }
+  int chunk = (K + splits - 1) / splits;
+  chunk = (chunk + BK - 1) / BK * BK;
+  if (chunk < BK) chunk = BK;
+  f.k_chunk = chunk;
+  f.splits = K > 0 ? (K + chunk - 1) / chunk : 1;
+  f.ws_bytes = f.splits > 1 ? (size_t)f.splits * P * Q * sizeof(float) : 0;
+  return f;
+}
+
+template <int WP, bool EXACT, bool VEC>
+int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
+  using L = SmemLayout<WP, EXACT>;
+  const size_t smem = L::bytes(p.lut_bytes);
+  int rc = ensure_smem(fgrad_gemm<WP, EXACT, VEC>, smem, device);
+  if (rc) return rc;
+  dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, p.splits);
+  fgrad_gemm<WP, EXACT, VEC><<<grid, L::NT, smem, st>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  if (p.splits > 1) {
+    const long long n = (long long)p.P * p.Q;
+    reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits);
+    CUDA_TRY(cudaGetLastError());
+  }
+  return AMSIM_OK;
+}
+
+int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_bytes, int device) {
+  if (p.P <= 0 || p.Q <= 0) return AMSIM_OK;
+  const FgradPlan f = plan_fgrad(p.P, p.Q, p.K, exact);
+  if (f.ws_bytes > 0) {
+    if (!ws || ws_bytes < f.ws_bytes)
+      return fail(AMSIM_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", f.ws_bytes, ws ? ws_bytes : (size_t)0);
+    if (!aligned16(ws)) return fail(AMSIM_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+  }
+  p.splits = f.splits;
+  p.k_chunk = f.k_chunk;
+  p.ws = static_cast<float*>(ws);
+  const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
+#define AMSIM_GO(WP_, EX_, VEC_) return launch_fgrad_t<WP_, EX_, VEC_>(st, p, device)
+  if (f.wp == 2) {
+    if (exact) { if (vec) AMSIM_GO(2, true, true); else AMSIM_GO(2, true, false); }
+    else       { if (vec) AMSIM_GO(2, false, true); else AMSIM_GO(2, false, false); }
+  } else {
+    if (exact) { if (vec) AMSIM_GO(1, true, true); else AMSIM_GO(1, true, false); }
+    else       { if (vec) AMSIM_GO(1, false, true); else AMSIM_GO(1, false, false); }
+  }
+#undef AMSIM_GO
+}
+
+int check_conv_dims(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w,
+                    int stride_h, int stride_w, int pad_top, int pad_left) {
+  if (batch < 0 || in_h <= 0 || in_w <= 0 || in_c <= 0 || f_h <= 0 || f_w <= 0 || out_c <= 0 || out_h < 0 ||
+      out_w < 0 || stride_h <= 0 || stride_w <= 0 || pad_top < 0 || pad_left < 0)
+    return fail(AMSIM_ERR_INVALID, "convolution dimensions must be positive (strides > 0, pads >= 0)");
+  if ((long long)f_h * f_w * (long long)(in_c > out_c ? in_c : out_c) >= (1ll << 30))
+    return fail(AMSIM_ERR_UNSUPPORTED, "reduction length exceeds 2^30");
+  if ((long long)batch * in_h * in_w >= (1ll << 31) - 256 || (long long)batch * out_h * out_w >= (1ll << 31) - 256)
+    return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 pixels");
+  return AMSIM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* amsim_last_error(void) { return g_err; }
+
+const char* amsim_version(void) { return "amsim 0.1 (sm_100a)"; }
+
+uint32_t amsim_debug_fastdiv(uint32_t n, uint32_t d) { return fdiv(n, make_fastdiv(d)); }
+
+int amsim_lut_open_bytes(const uint8_t* bytes, int m, int device, amsim_lut** out) {
+  if (!bytes || !out) return fail(AMSIM_ERR_INVALID, "NULL argument");
+  if (m < 1 || m > 11) return fail(AMSIM_ERR_LUT_NAME, "mantissa width %d outside 1..11", m);
+  return upload_lut(bytes, m, device, out);
+}
+
+int amsim_lut_open(const char* path, int device, amsim_lut** out) {
+  if (!path || !out) return fail(AMSIM_ERR_INVALID, "NULL argument");
+  if (!*path) return fail(AMSIM_ERR_LUT_NAME, "no mant lut file name given");
+  const int m = parse_mant_width(path);
+  if (m < 0) return fail(AMSIM_ERR_LUT_NAME, "cannot take a mantissa width in 1..11 from '%s' (expected <MODEL>_<m>.bin)", path);
+  char real[PATH_MAX];
+  if (!realpath(path, real)) return fail(AMSIM_ERR_LUT_IO, "lut file '%s' cannot be opened", path);
+  const std::string key = std::string(real) + "@" + std::to_string(device);
+  std::lock_guard<std::mutex> lk(g_lut_mu);
+  auto it = g_lut_cache.find(key);
+  if (it != g_lut_cache.end()) {
+    it->second->refs++;
+    *out = it->second;
+    return AMSIM_OK;
+  }
+  FILE* f = fopen(real, "rb");
+  if (!f) return fail(AMSIM_ERR_LUT_IO, "lut file '%s' cannot be opened", path);
+  const size_t want = (size_t)1 << (2 * m);
+  std::vector<uint8_t> buf(want + 1);
+  const size_t got = fread(buf.data(), 1, want + 1, f);
+  fclose(f);
+  if (got != want)
+    return fail(AMSIM_ERR_LUT_SIZE, "lut file '%s' holds %s%zu bytes, m = %d needs exactly %zu", path,
+                got > want ? "more than " : "", got > want ? want : got, m, want);
+  amsim_lut* h = nullptr;
+  const int rc = upload_lut(buf.data(), m, device, &h);
+  if (rc) return rc;
+  h->key = key;
+  g_lut_cache[key] = h;
+  *out = h;
+  return AMSIM_OK;
+}
+
+int amsim_lut_close(amsim_lut* lut) {
+  if (!lut) return AMSIM_OK;
+  std::lock_guard<std::mutex> lk(g_lut_mu);
+  if (--lut->refs > 0) return AMSIM_OK;
+  if (!lut->key.empty()) g_lut_cache.erase(lut->key);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(lut->device);
+  cudaFree(lut->d_raw);
+  cudaFree(lut->d_canon);
+  cudaFree(lut->d_trans);
+  cudaSetDevice(prev);
+  delete lut;
+  return AMSIM_OK;
+}
+
+int amsim_lut_info(const amsim_lut* lut, int* mant_width, uint32_t* mant_mask, int* a_shift, int* b_shift,
+                   const uint8_t** device_bytes) {
+  if (!lut) return fail(AMSIM_ERR_INVALID, "lut handle is NULL");
+  if (mant_width) *mant_width = lut->m;
+  if (mant_mask) *mant_mask = ((1u << lut->m) - 1u) << (23 - lut->m);  // approx_mul_lut.h:28
+  if (a_shift) *a_shift = 23 - 2 * lut->m;                             // :26
+  if (b_shift) *b_shift = 23 - lut->m;                                 // :27
+  if (device_bytes) *device_bytes = lut->d_raw;
+  return AMSIM_OK;
+}
+
+int amsim_mul(void* stream, const amsim_lut* lut, const float* a, const float* b, float* out, size_t n) {
+  int rc = check_common(lut, 0, false);
+  if (rc) return rc;
+  if (n == 0) return AMSIM_OK;
+  if (!a || !b || !out) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  size_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  mul_elementwise<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, lut->d_raw, lut->m);
+  CUDA_TRY(cudaGetLastError());
+  return AMSIM_OK;
+}
+
+int amsim_conv2d_geometry(int in_h, int in_w, int f_h, int f_w, int stride_h, int stride_w, int same, int* out_h,
+                          int* out_w, int* pad_top, int* pad_left) {
+  if (in_h <= 0 || in_w <= 0 || f_h <= 0 || f_w <= 0 || stride_h <= 0 || stride_w <= 0)
+    return fail(AMSIM_ERR_INVALID, "geometry arguments must be positive");
+  auto one = [&](int in, int f, int s, int* o, int* pb) -> int {
+    if (same) {
+      *o = (in + s - 1) / s;
+      int total = (*o - 1) * s + f - in;
+      *pb = total > 0 ? total / 2 : 0;
+    } else {
+      if (in < f) return 1;
+      *o = (in - f + s) / s;
+      *pb = 0;
+    }
+    return 0;
+  };
+  int oh, ow, pt, pl;
+  if (one(in_h, f_h, stride_h, &oh, &pt) || one(in_w, f_w, stride_w, &ow, &pl))
+    return fail(AMSIM_ERR_INVALID, "VALID padding needs the filter to fit inside the input");
+  if (out_h) *out_h = oh;
+  if (out_w) *out_w = ow;
+  if (pad_top) *pad_top = pt;
+  if (pad_left) *pad_left = pl;
+  return AMSIM_OK;
+}
+
+int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x, const float* w, float* y, int batch, int in_h,
+                     int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w, int stride_h, int stride_w,
+                     int pad_top, int pad_left, unsigned flags) {
+  int rc = check_common(lut, flags, true);
+  if (rc) return rc;
+  rc = check_conv_dims(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h, stride_w, pad_top, pad_left);
+  if (rc) return rc;
+  if (batch == 0 || out_h == 0 || out_w == 0) return AMSIM_OK;
+  if (!x || !w || !y) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  Params p{};
+  p.V = x; p.U = w; p.O = y;
+  p.P = batch * out_h * out_w; p.Q = out_c; p.K = f_h * f_w * in_c;
+  Gather& g = p.g;
+  g.PH = out_h; g.PW = out_w; g.ps_h = stride_h; g.ps_w = stride_w; g.off_t = pad_top; g.off_l = pad_left;
+  g.lim_h = in_h; g.lim_w = in_w; g.dil_h = 1; g.dil_w = 1; g.SH = in_h; g.SW = in_w; g.SC = in_c; g.KW = f_w;
+  fill_gather_divs(g);
+  p.taps = f_h * f_w; p.u_flip = 0; p.u_tap = (long long)in_c * out_c; p.u_sk = out_c; p.u_sq = 1;
+  p.o_sp = out_c; p.o_sq = 1;
+  fill_lut(p, lut, /*v_is_first_operand=*/true);
+  return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
+}
+
+int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, const float* dy, float* dx, int batch,
+                           int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w,
+                           int stride_h, int stride_w, int pad_top, int pad_left, unsigned flags) {
+  int rc = check_common(lut, flags, true);
+  if (rc) return rc;
+  rc = check_conv_dims(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h, stride_w, pad_top, pad_left);
+  if (rc) return rc;
+  if (batch == 0) return AMSIM_OK;
+  if (!dy || !w || !dx) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  if (out_h == 0 || out_w == 0) return fail(AMSIM_ERR_INVALID, "empty output gradient");
+  if (pad_top > f_h - 1 || pad_left > f_w - 1) return fail(AMSIM_ERR_INVALID, "forward padding exceeds filter size - 1");
+  Params p{};
+  p.V = dy; p.U = w; p.O = dx;
+  p.P = batch * in_h * in_w; p.Q = in_c; p.K = f_h * f_w * out_c;
+  Gather& g = p.g;
+  // convam.cc:1066-1067, 1083-1084
+  g.PH = in_h; g.PW = in_w; g.ps_h = 1; g.ps_w = 1; g.off_t = f_h - 1 - pad_top; g.off_l = f_w - 1 - pad_left;
+  g.lim_h = (out_h - 1) * stride_h + 1; g.lim_w = (out_w - 1) * stride_w + 1;
+  g.dil_h = stride_h; g.dil_w = stride_w; g.SH = out_h; g.SW = out_w; g.SC = out_c; g.KW = f_w;
+  fill_gather_divs(g);
+  // flipped filter with in/out channels swapped: element (tap, ko; c)
+  p.taps = f_h * f_w; p.u_flip = 1; p.u_tap = (long long)in_c * out_c; p.u_sk = 1; p.u_sq = out_c;
+  p.o_sp = in_c; p.o_sq = 1;
+  fill_lut(p, lut, true);
+  return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
+}
+
+size_t amsim_conv2d_bwd_filter_workspace(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c,
+                                         int out_h, int out_w, unsigned flags) {
+  (void)in_h; (void)in_w;
+  if (batch <= 0 || in_c <= 0 || f_h <= 0 || f_w <= 0 || out_c <= 0 || out_h <= 0 || out_w <= 0) return 0;
+  return plan_fgrad(f_h * f_w * in_c, out_c, batch * out_h * out_w, flags & AMSIM_DETERMINISTIC).ws_bytes;
+}
+
+int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, const float* dy, float* dw, int batch,
+                            int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w,
+                            int stride_h, int stride_w, int pad_top, int pad_left, void* workspace,
+                            size_t workspace_bytes, unsigned flags) {
+  int rc = check_common(lut, flags, true);
+  if (rc) return rc;
+  rc = check_conv_dims(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h, stride_w, pad_top, pad_left);
+  if (rc) return rc;
+  if (!dw) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  const long long npix = (long long)batch * out_h * out_w;
+  if (npix == 0) {  // empty reduction: the gradient is all zeros
+    CUDA_TRY(cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)f_h * f_w * in_c * out_c, (cudaStream_t)stream));
+    return AMSIM_OK;
+  }
+  if (!x || !dy) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  Params p{};
+  p.V = x; p.U = dy; p.O = dw;
+  p.P = f_h * f_w * in_c; p.Q = out_c; p.K = (int)npix;
+  Gather& g = p.g;
+  g.PH = out_h; g.PW = out_w; g.ps_h = stride_h; g.ps_w = stride_w; g.off_t = pad_top; g.off_l = pad_left;
+  g.lim_h = in_h; g.lim_w = in_w; g.dil_h = 1; g.dil_w = 1; g.SH = in_h; g.SW = in_w; g.SC = in_c; g.KW = f_w;
+  fill_gather_divs(g);
+  p.u_sk = out_c; p.u_sq = 1;
+  fill_lut(p, lut, true);
+  return launch_fgrad((cudaStream_t)stream, p, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
+}
+
+static void dense_gather(Gather& g, int width) {
+  g.PH = 1; g.PW = 1; g.ps_h = 1; g.ps_w = 1; g.off_t = 0; g.off_l = 0; g.lim_h = 1; g.lim_w = 1;
+  g.dil_h = 1; g.dil_w = 1; g.SH = 1; g.SW = 1; g.SC = width; g.KW = 1;
+  fill_gather_divs(g);
+}
+
+static int check_dense(int batch, int units, int input_width) {
+  if (batch < 0 || units <= 0 || input_width <= 0) return fail(AMSIM_ERR_INVALID, "dense dimensions must be positive");
+  return AMSIM_OK;
+}
+
+int amsim_dense_fwd(void* stream, const amsim_lut* lut, const float* x, const float* w, float* y, int batch, int units,
+                    int input_width, unsigned flags) {
+  int rc = check_common(lut, flags, true);
+  if (rc) return rc;
+  if ((rc = check_dense(batch, units, input_width))) return rc;
+  if (batch == 0) return AMSIM_OK;
+  if (!x || !w || !y) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  Params p{};
+  p.V = x; p.U = w; p.O = y;
+  p.P = batch; p.Q = units; p.K = input_width;
+  dense_gather(p.g, input_width);
+  p.taps = 1; p.u_flip = 0; p.u_tap = 0; p.u_sk = units; p.u_sq = 1;
+  p.o_sp = units; p.o_sq = 1;
+  fill_lut(p, lut, true);
+  return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
+}
+
+int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w, const float* g_, float* dx, int batch,
+                          int units, int input_width, unsigned flags) {
+  int rc = check_common(lut, flags, true);
+  if (rc) return rc;
+  if ((rc = check_dense(batch, units, input_width))) return rc;
+  if (batch == 0) return AMSIM_OK;
+  if (!w || !g_ || !dx) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  // dx[b,k] = sum_u AM(w[k,u], g[b,u]) — denseam_kernel.cu:84-94: the weight is
+  // the multiplier's FIRST operand, the gradient (lane operand here) the second.
+  Params p{};
+  p.V = g_; p.U = w; p.O = dx;
+  p.P = batch; p.Q = input_width; p.K = units;
+  dense_gather(p.g, units);
+  p.taps = 1; p.u_flip = 0; p.u_tap = 0; p.u_sk = 1; p.u_sq = units;
+  p.o_sp = input_width; p.o_sq = 1;
+  fill_lut(p, lut, /*v_is_first_operand=*/false);
+  return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
+}
+
+size_t amsim_dense_bwd_weight_workspace(int batch, int units, int input_width, unsigned flags) {
+  if (batch <= 0 || units <= 0 || input_width <= 0) return 0;
+  return plan_fgrad(input_width, units, batch, flags & AMSIM_DETERMINISTIC).ws_bytes;
+}
+
+int amsim_dense_bwd_weight(void* stream, const amsim_lut* lut, const float* x, const float* g_, float* dw, int batch,
+                           int units, int input_width, void* workspace, size_t workspace_bytes, unsigned flags) {
+  int rc = check_common(lut, flags, true);
+  if (rc) return rc;
+  if ((rc = check_dense(batch, units, input_width))) return rc;
+  if (!dw) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  if (batch == 0) {
+    CUDA_TRY(cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)input_width * units, (cudaStream_t)stream));
+    return AMSIM_OK;
+  }
+  if (!x || !g_) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  // dw[k,u] = sum_b AM(x[b,k], g[b,u]) — the filter gradient of a 1x1
+  // convolution over a batch x 1 x 1 grid.
+  Params p{};
+  p.V = x; p.U = g_; p.O = dw;
+  p.P = input_width; p.Q = units; p.K = batch;
+  Gather& g = p.g;
+  g.PH = 1; g.PW = 1; g.ps_h = 1; g.ps_w = 1; g.off_t = 0; g.off_l = 0; g.lim_h = 1; g.lim_w = 1;
+  g.dil_h = 1; g.dil_w = 1; g.SH = 1; g.SW = 1; g.SC = input_width; g.KW = 1;
+  fill_gather_divs(g);
+  p.u_sk = units; p.u_sq = 1;
+  fill_lut(p, lut, true);
+  return launch_fgrad((cudaStream_t)stream, p, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
+}
+
+int amsim_matmul(void* stream, const amsim_lut* lut, const float* a, const float* b, float* c, int batch_a,
+                 int batch_b, int row_a, int col_a, int row_b, int col_b, unsigned flags) {
+  int rc = check_common(lut, flags, true);
+  if (rc) return rc;
+  if (batch_a < 0 || batch_b < 0 || row_a < 0 || col_a < 0 || row_b < 0 || col_b < 0)
+    return fail(AMSIM_ERR_INVALID, "negative matrix dimension");
+  if (col_a != row_b) return fail(AMSIM_ERR_INVALID, "Does not meet cols of mat a is equal rows of mat b");
+  if (batch_a > 1 && batch_b > 1 && batch_a != batch_b)
+    return fail(AMSIM_ERR_INVALID, "Does not meet batch of mat a is equal batch of matb");
+  int nb = batch_a > batch_b ? batch_a : batch_b;
+  if (nb == 0) nb = 1;
+  if (row_a == 0 || col_b == 0) return AMSIM_OK;
+  if (!c) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  if (col_a == 0) {  // [x,0] x [0,y]: zeros (matmulam.cc:156-161)
+    CUDA_TRY(cudaMemsetAsync(c, 0, sizeof(float) * (size_t)nb * row_a * col_b, (cudaStream_t)stream));
+    return AMSIM_OK;
+  }
+  if (!a || !b) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  Params p{};
+  p.V = a; p.U = b; p.O = c;
+  p.P = row_a; p.Q = col_b; p.K = col_a;
+  dense_gather(p.g, col_a);
+  p.taps = 1; p.u_flip = 0; p.u_tap = 0; p.u_sk = col_b; p.u_sq = 1;
+  p.o_sp = col_b; p.o_sq = 1;
+  p.v_bs = batch_a > 1 ? (long long)row_a * col_a : 0;
+  p.u_bs = batch_b > 1 ? (long long)row_b * col_b : 0;
+  p.o_bs = (long long)row_a * col_b;
+  fill_lut(p, lut, true);
+  return launch_gather((cudaStream_t)stream, p, nb, flags & AMSIM_DETERMINISTIC, lut->device);
+}
+
+}  // extern "C"

@@ -1,0 +1,582 @@
+// LUT-GEMM kernels for the AM-Simulator path, written for sm_100a.
+//
+// Every op of the path is one of two kernels over an abstract product
+//     Out[p, q] = sum_k AM(V[p, k], U[k, q])
+// where V is the operand that varies across the lanes of a warp and U the one
+// that is uniform across a warp:
+//
+//   gather_gemm  V is gathered along k (NHWC patch rows, dense rows): conv
+//                forward, conv input gradient, dense forward / input gradient,
+//                batched matmul.  One ascending-k FP32 chain per output.
+//   fgrad_gemm   V is gathered along p (channels of one filter tap) and the
+//                reduction runs over output pixels: conv filter gradient and
+//                dense weight gradient, optionally split along k.
+//
+// Why this shape.  Each product needs one byte from a 2^m x 2^m table.  The
+// table sits in shared memory with one row per value of the WARP-UNIFORM
+// operand (row = 2^m bytes + a zero column, at most 132 bytes), so the 32 byte
+// reads of one LDS all fall into a single 128-byte-wide bank row (plus at most
+// one wrap-around word) and are served in one wavefront: the table lookup is
+// conflict free by construction, whatever the data.  The inner loop per product
+// is: address add, LDS.U8, integer multiply-add that rebuilds the product's
+// significand/exponent bits next to the lane operand's sign+exponent, and one
+// FFMA with the uniform operand's power of two (the product of a float and a
+// power of two is exact, so the FFMA rounds exactly like the reference's
+// "accumulator + product" add).  Tensor cores cannot be used: no product is a
+// hardware multiply.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace amsim {
+
+constexpr int BK = 16;  // reduction steps per shared-memory stage
+constexpr int BQ = 64;  // q extent of a CTA tile (4 warps x 16)
+constexpr int TR = 16;  // q values per warp, held as registers
+constexpr int TC = 4;   // consecutive p values per lane
+
+// Division by a run-time constant: n / d for n < 2^31.
+struct FastDiv {
+  uint32_t mul, shr, d;
+};
+
+inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  f.d = d ? d : 1;
+  if (f.d == 1) {
+    f.mul = 0;
+    f.shr = 0;
+    return f;
+  }
+  uint32_t lg = 0;
+  while ((1ull << lg) < f.d) ++lg;  // ceil(log2 d)
+  const uint32_t p = 31 + lg;
+  f.mul = (uint32_t)(((1ull << p) + f.d - 1) / f.d);
+  f.shr = p - 32;
+  return f;
+}
+
+__host__ __device__ __forceinline__ uint32_t fdiv(uint32_t n, const FastDiv& f) {
+#ifdef __CUDA_ARCH__
+  return f.d == 1 ? n : (__umulhi(n, f.mul) >> f.shr);
+#else
+  return f.d == 1 ? n : (uint32_t)(((uint64_t)n * f.mul) >> 32) >> f.shr;
+#endif
+}
+
+// How a flat index decomposes into (image, row, col) of a grid, and how a
+// filter tap displaces it into the source tensor.  Covers the forward patch
+// gather (cuda_kernel.cu:39-58 of the reference), the stride-dilated,
+// back-padded gather of the input gradient (:467-500) and the filter-gradient
+// gather (:331-350).
+struct Gather {
+  int PH, PW;          // grid the flat index runs over
+  int ps_h, ps_w;      // grid step in source coordinates
+  int off_t, off_l;    // padding subtracted
+  int lim_h, lim_w;    // source coordinate must be in [0, lim)
+  int dil_h, dil_w;    // ... and a multiple of this (1 except input gradient)
+  int SH, SW, SC;      // source tensor rows, cols, channels
+  int KW;              // filter columns (tap = kh * KW + kw)
+  FastDiv d_img, d_pw, d_sc, d_kw, d_dh, d_dw;
+};
+
+struct Params {
+  const float* V;
+  const float* U;
+  float* O;
+  int P, Q, K;  // extents of p, q and the reduction
+  Gather g;
+  // U element for reduction index k = tap * g.SC + kk and column q sits at
+  //   U[tap' * u_tap + kk * u_sk + q * u_sq], tap' = taps-1-tap if u_flip
+  // (the flip folds cuda/reverseNswapdim23.cu into the index map).
+  long long u_tap;
+  int u_sk, u_sq, u_flip, taps;
+  long long o_sp, o_sq;         // Out[p, q] at O[p * o_sp + q * o_sq]
+  long long v_bs, u_bs, o_bs;   // per-blockIdx.z (batch) offsets
+  const uint8_t* lut;           // encoded table, rows of `rowstride` bytes
+  int lut_bytes;                // multiple of 16
+  int m;
+  uint32_t mult;                // 1 << (23 - m)
+  uint32_t rowstride;           // (1 << m) + 4
+  // fgrad only
+  int k_chunk, splits;
+  float* ws;                    // [splits][P][Q] partial sums when splits > 1
+};
+
+__device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
+  uint32_t v;
+  asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
+  return v;
+}
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// ---- operand encodings -------------------------------------------------------
+// Lane operand (V): one word = sign+exponent bits | table column.
+//   fast:  a zero exponent field selects the all-zero table column and drops
+//          the sign/exponent, so the rebuilt factor is exactly 0.
+//   exact: the raw fields, nothing special-cased (the reference pushes zeros
+//          and denormals through the table like any other value).
+template <bool EXACT>
+__device__ __forceinline__ uint32_t enc_v(uint32_t bits, int m) {
+  const uint32_t idx = (bits >> (23 - m)) & ((1u << m) - 1u);
+  const uint32_t w = (bits & 0xFF800000u) | idx;
+  if (EXACT) return w;
+  return (bits & 0x7F800000u) ? w : (1u << m);
+}
+
+// One reduction step of a 16 (q) x 4 (p) register tile.
+//   vrow : 4 consecutive lane-operand words
+//   uP   : 16 uniform-operand sign+exponent words (as floats: +-2^(e-127))
+//   uR   : 16 shared-memory byte addresses of the uniform operand's table row
+//   uE   : exact mode only, 16 exponent fields (e << 23)
+template <bool EXACT>
+__device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* __restrict__ vrow,
+                                         const uint32_t* __restrict__ uP,
+                                         const uint32_t* __restrict__ uR,
+                                         const uint32_t* __restrict__ uE, const uint32_t mult) {
+  const uint4 cw = *reinterpret_cast<const uint4*>(vrow);
+  const uint32_t w[TC] = {cw.x, cw.y, cw.z, cw.w};
+  uint32_t ci[TC], cs[TC];
+  int cn[TC];
+#pragma unroll
+  for (int t = 0; t < TC; ++t) {
+    ci[t] = w[t] & 0x1FFu;
+    if (EXACT) {
+      // AMsimulator.inl:26-33: exponent sum - 127, folded into the lane word
+      cs[t] = (w[t] & 0xFF800000u) - 0x3F800000u;
+      cn[t] = (int)(0x3F800000u - (w[t] & 0x7F800000u));
+    } else {
+      cs[t] = w[t] & 0xFF800000u;
+    }
+  }
+#pragma unroll
+  for (int g4 = 0; g4 < TR / 4; ++g4) {
+    const uint4 p4 = *reinterpret_cast<const uint4*>(uP + 4 * g4);
+    const uint4 r4 = *reinterpret_cast<const uint4*>(uR + 4 * g4);
+    const uint32_t pp[4] = {p4.x, p4.y, p4.z, p4.w};
+    const uint32_t rr[4] = {r4.x, r4.y, r4.z, r4.w};
+    uint32_t ee[4] = {0, 0, 0, 0};
+    if (EXACT) {
+      const uint4 e4 = *reinterpret_cast<const uint4*>(uE + 4 * g4);
+      ee[0] = e4.x; ee[1] = e4.y; ee[2] = e4.z; ee[3] = e4.w;
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+#pragma unroll
+      for (int t = 0; t < TC; ++t) {
+        const uint32_t v = lds_u8(rr[r] + ci[t]);
+        if (EXACT) {
+          // bits = sign + ((ea + eb - 127 + carry) << 23) + mantissa, uint32 wrap
+          const uint32_t bits = v * mult + (pp[r] + cs[t]);
+          // product is +0 when ea + eb <= 127 (AMsimulator.inl:28); adding +0
+          // never changes a non-negative-zero accumulator, so skip the add.
+          if ((int)ee[r] > cn[t]) acc[4 * g4 + r][t] = __fadd_rn(acc[4 * g4 + r][t], __uint_as_float(bits));
+        } else {
+          const float y = __uint_as_float(v * mult + cs[t]);
+          acc[4 * g4 + r][t] = __fmaf_rn(__uint_as_float(pp[r]), y, acc[4 * g4 + r][t]);
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void copy_lut_to_smem(uint8_t* lut_s, const uint8_t* __restrict__ lut, int bytes,
+                                                 int tid, int nthreads) {
+  const uint4* src = reinterpret_cast<const uint4*>(lut);
+  uint4* dst = reinterpret_cast<uint4*>(lut_s);
+  for (int i = tid; i < bytes / 16; i += nthreads) dst[i] = __ldg(src + i);
+}
+
+// Stores the uniform-operand (U) words of one element.
+template <bool EXACT>
+__device__ __forceinline__ void store_u(uint32_t* uP, uint32_t* uR, uint32_t* uE, int at, uint32_t bits,
+                                        const Params& prm, uint32_t lut_base) {
+  const uint32_t idx = (bits >> (23 - prm.m)) & ((1u << prm.m) - 1u);
+  uP[at] = bits & 0xFF800000u;
+  uR[at] = lut_base + idx * prm.rowstride;
+  if (EXACT) uE[at] = bits & 0x7F800000u;
+}
+
+template <int WP, bool EXACT>
+struct SmemLayout {
+  static constexpr int NT = WP * 128;
+  static constexpr int BP = WP * 128;
+  static constexpr int VS = BP + 4;  // padded row: conflict-free 4-row scatter
+  static constexpr int V_WORDS = 2 * BK * VS;
+  static constexpr int U_WORDS = 2 * BK * BQ;
+  static constexpr int WORDS = V_WORDS + U_WORDS * (EXACT ? 3 : 2);
+  static size_t bytes(int lut_bytes) { return (size_t)lut_bytes + (size_t)WORDS * 4; }
+};
+
+// -----------------------------------------------------------------------------
+// gather_gemm: V gathered along k.  grid = (ceil(P/BP), ceil(Q/64), batch).
+// -----------------------------------------------------------------------------
+template <int WP, bool EXACT, bool VEC>
+__global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) gather_gemm(const Params prm) {
+  using L = SmemLayout<WP, EXACT>;
+  constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
+  constexpr int NU = BK * BQ / NT;  // U elements staged per thread
+
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint8_t* lut_s = smem;
+  uint32_t* Vs = reinterpret_cast<uint32_t*>(smem + prm.lut_bytes);
+  uint32_t* UsP = Vs + L::V_WORDS;
+  uint32_t* UsR = UsP + L::U_WORDS;
+  uint32_t* UsE = UsR + L::U_WORDS;
+
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  const int wp = w % WP, wq = w / WP;
+  const int p0 = blockIdx.x * BP, q0 = blockIdx.y * BQ;
+  const float* __restrict__ Vg = prm.V + (long long)blockIdx.z * prm.v_bs;
+  const float* __restrict__ Ug = prm.U + (long long)blockIdx.z * prm.u_bs;
+  float* __restrict__ Og = prm.O + (long long)blockIdx.z * prm.o_bs;
+  const Gather& g = prm.g;
+
+  copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+  const uint32_t lut_base = smem_addr(lut_s);
+
+  // ---- this thread's share of the V tile: 2 rows (p) x 2 groups of 4 k ------
+  int pl[2], r0[2], c0[2];
+  long long nb[2];
+  bool pv[2];
+#pragma unroll
+  for (int ip = 0; ip < 2; ++ip) {
+    pl[ip] = (ip * 4 * WP + w) * 16 + (lane & 15);
+    const uint32_t pg = (uint32_t)(p0 + pl[ip]);
+    pv[ip] = pg < (uint32_t)prm.P;
+    const uint32_t n = fdiv(pg, g.d_img);
+    const uint32_t rem = pg - n * (uint32_t)(g.PH * g.PW);
+    const uint32_t a = fdiv(rem, g.d_pw);
+    const uint32_t b = rem - a * (uint32_t)g.PW;
+    r0[ip] = (int)a * g.ps_h - g.off_t;
+    c0[ip] = (int)b * g.ps_w - g.off_l;
+    nb[ip] = (long long)n * ((long long)g.SH * g.SW * g.SC);
+  }
+  const int kg_sub = lane >> 4;
+
+  float4 vraw[2][2];  // [k group][row]
+  float uraw[NU];
+
+  auto load_tile = [&](int kb) {
+#pragma unroll
+    for (int ik = 0; ik < 2; ++ik) {
+      const int kglob = kb * BK + 4 * (2 * ik + kg_sub);
+      if (VEC) {
+        const uint32_t tap = fdiv((uint32_t)kglob, g.d_sc);
+        const int ch = kglob - (int)tap * g.SC;
+        const int kh = (int)fdiv(tap, g.d_kw);
+        const int kw = (int)tap - kh * g.KW;
+#pragma unroll
+        for (int ip = 0; ip < 2; ++ip) {
+          float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+          const int u = r0[ip] + kh, v = c0[ip] + kw;
+          if (pv[ip] && kglob < prm.K && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
+            const int row = (int)fdiv((uint32_t)u, g.d_dh), col = (int)fdiv((uint32_t)v, g.d_dw);
+            if (row * g.dil_h == u && col * g.dil_w == v)
+              val = __ldg(reinterpret_cast<const float4*>(Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch)));
+          }
+          vraw[ik][ip] = val;
+        }
+      } else {
+        float tmp[2][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kj = kglob + j;
+          const uint32_t tap = fdiv((uint32_t)kj, g.d_sc);
+          const int ch = kj - (int)tap * g.SC;
+          const int kh = (int)fdiv(tap, g.d_kw);
+          const int kw = (int)tap - kh * g.KW;
+#pragma unroll
+          for (int ip = 0; ip < 2; ++ip) {
+            float val = 0.f;
+            const int u = r0[ip] + kh, v = c0[ip] + kw;
+            if (pv[ip] && kj < prm.K && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
+              const int row = (int)fdiv((uint32_t)u, g.d_dh), col = (int)fdiv((uint32_t)v, g.d_dw);
+              if (row * g.dil_h == u && col * g.dil_w == v)
+                val = __ldg(Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch));
+            }
+            tmp[ip][j] = val;
+          }
+        }
+#pragma unroll
+        for (int ip = 0; ip < 2; ++ip) vraw[ik][ip] = make_float4(tmp[ip][0], tmp[ip][1], tmp[ip][2], tmp[ip][3]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NU; ++j) {
+      const int e = j * NT + t;
+      const int kglob = kb * BK + (e >> 6), qg = q0 + (e & 63);
+      float val = 0.f;
+      if (kglob < prm.K && qg < prm.Q) {
+        const uint32_t tap = fdiv((uint32_t)kglob, g.d_sc);
+        const int kk = kglob - (int)tap * g.SC;
+        const int tp = prm.u_flip ? prm.taps - 1 - (int)tap : (int)tap;
+        val = __ldg(Ug + (long long)tp * prm.u_tap + (long long)kk * prm.u_sk + (long long)qg * prm.u_sq);
+      }
+      uraw[j] = val;
+    }
+  };
+
+  auto store_tile = [&](int buf) {
+    uint32_t* vs = Vs + buf * BK * VS;
+#pragma unroll
+    for (int ik = 0; ik < 2; ++ik) {
+      const int krow = 4 * (2 * ik + kg_sub);
+#pragma unroll
+      for (int ip = 0; ip < 2; ++ip) {
+        const float4 f = vraw[ik][ip];
+        vs[(krow + 0) * VS + pl[ip]] = enc_v<EXACT>(__float_as_uint(f.x), prm.m);
+        vs[(krow + 1) * VS + pl[ip]] = enc_v<EXACT>(__float_as_uint(f.y), prm.m);
+        vs[(krow + 2) * VS + pl[ip]] = enc_v<EXACT>(__float_as_uint(f.z), prm.m);
+        vs[(krow + 3) * VS + pl[ip]] = enc_v<EXACT>(__float_as_uint(f.w), prm.m);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NU; ++j) {
+      const int e = j * NT + t;
+      store_u<EXACT>(UsP + buf * BK * BQ, UsR + buf * BK * BQ, UsE + buf * BK * BQ, e, __float_as_uint(uraw[j]), prm,
+                     lut_base);
+    }
+  };
+
+  float acc[TR][TC];
+#pragma unroll
+  for (int r = 0; r < TR; ++r)
+#pragma unroll
+    for (int c = 0; c < TC; ++c) acc[r][c] = 0.f;
+
+  const int nkb = (prm.K + BK - 1) / BK;
+  load_tile(0);
+  store_tile(0);
+  __syncthreads();
+
+  const int vcol = wp * 128 + 4 * lane;
+  const int ucol = wq * TR;
+  for (int kb = 0; kb < nkb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < nkb) load_tile(kb + 1);
+    const uint32_t* vs = Vs + buf * BK * VS + vcol;
+    const uint32_t* up = UsP + buf * BK * BQ + ucol;
+    const uint32_t* ur = UsR + buf * BK * BQ + ucol;
+    const uint32_t* ue = UsE + buf * BK * BQ + ucol;
+#pragma unroll 2
+    for (int kk = 0; kk < BK; ++kk)
+      mac_step<EXACT>(acc, vs + kk * VS, up + kk * BQ, ur + kk * BQ, ue + kk * BQ, prm.mult);
+    if (kb + 1 < nkb) store_tile(buf ^ 1);
+    __syncthreads();
+  }
+
+  // ---- epilogue ---------------------------------------------------------------
+  const bool vec_out = prm.o_sq == 1 && (prm.o_sp & 3) == 0 && (prm.o_bs & 3) == 0 &&
+                       ((reinterpret_cast<uintptr_t>(prm.O) & 15) == 0);
+#pragma unroll
+  for (int c = 0; c < TC; ++c) {
+    const int pg = p0 + vcol + c;
+    if (pg >= prm.P) continue;
+    float* orow = Og + (long long)pg * prm.o_sp;
+#pragma unroll
+    for (int g4 = 0; g4 < TR / 4; ++g4) {
+      const int qg = q0 + ucol + 4 * g4;
+      if (vec_out && qg + 3 < prm.Q) {
+        *reinterpret_cast<float4*>(orow + qg) =
+            make_float4(acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          if (qg + r < prm.Q) orow[(long long)(qg + r) * prm.o_sq] = acc[4 * g4 + r][c];
+      }
+    }
+  }
+}
+
+// -----------------------------------------------------------------------------
+// fgrad_gemm: p = (tap, channel) gathered along p, q = output channel, the
+// reduction index k runs over grid positions (n, oh, ow).
+// grid = (ceil(P/BP), ceil(Q/64), splits); split s reduces
+// k in [s * k_chunk, min((s+1) * k_chunk, K)) and writes ws[s] (or O if there
+// is only one split).
+// -----------------------------------------------------------------------------
+template <int WP, bool EXACT, bool VEC>
+__global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) fgrad_gemm(const Params prm) {
+  using L = SmemLayout<WP, EXACT>;
+  constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
+  constexpr int NU = BK * BQ / NT;
+  constexpr int GPR = BP / 4;        // 4-wide p groups per k row
+  constexpr int RPP = NT / GPR;      // k rows covered per pass (= 4)
+  constexpr int NV = BK / RPP;       // passes (= 4)
+
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint8_t* lut_s = smem;
+  uint32_t* Vs = reinterpret_cast<uint32_t*>(smem + prm.lut_bytes);
+  uint32_t* UsP = Vs + L::V_WORDS;
+  uint32_t* UsR = UsP + L::U_WORDS;
+  uint32_t* UsE = UsR + L::U_WORDS;
+
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  const int wp = w % WP, wq = w / WP;
+  const int p0 = blockIdx.x * BP, q0 = blockIdx.y * BQ;
+  const int kbeg = blockIdx.z * prm.k_chunk;
+  const int kend = min(kbeg + prm.k_chunk, prm.K);
+  const Gather& g = prm.g;
+  const float* __restrict__ Vg = prm.V;
+  const float* __restrict__ Ug = prm.U;
+
+  copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+  const uint32_t lut_base = smem_addr(lut_s);
+
+  // ---- this thread's 4 consecutive p (same for every k row it stages) ---------
+  const int pl = 4 * (t % GPR);
+  const int krow0 = t / GPR;
+  int kh[4], kw[4], ch[4];
+  bool pv[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t pg = (uint32_t)(p0 + pl + j);
+    pv[j] = pg < (uint32_t)prm.P;
+    const uint32_t tap = fdiv(pg, g.d_sc);
+    ch[j] = (int)(pg - tap * (uint32_t)g.SC);
+    kh[j] = (int)fdiv(tap, g.d_kw);
+    kw[j] = (int)tap - kh[j] * g.KW;
+  }
+
+  float4 vraw[NV];
+  float uraw[NU];
+
+  auto load_tile = [&](int kb) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int pix = kbeg + kb * BK + i * RPP + krow0;
+      float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (pix < kend) {
+        const uint32_t n = fdiv((uint32_t)pix, g.d_img);
+        const uint32_t rem = (uint32_t)pix - n * (uint32_t)(g.PH * g.PW);
+        const uint32_t a = fdiv(rem, g.d_pw);
+        const uint32_t b = rem - a * (uint32_t)g.PW;
+        const int r0 = (int)a * g.ps_h - g.off_t, c0 = (int)b * g.ps_w - g.off_l;
+        const float* src = Vg + (long long)n * ((long long)g.SH * g.SW * g.SC);
+        if (VEC) {
+          const int u = r0 + kh[0], v = c0 + kw[0];
+          if (pv[0] && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
+            val = __ldg(reinterpret_cast<const float4*>(src + ((long long)(u * g.SW + v) * g.SC + ch[0])));
+        } else {
+          float tmp[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int u = r0 + kh[j], v = c0 + kw[j];
+            tmp[j] = 0.f;
+            if (pv[j] && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
+              tmp[j] = __ldg(src + ((long long)(u * g.SW + v) * g.SC + ch[j]));
+          }
+          val = make_float4(tmp[0], tmp[1], tmp[2], tmp[3]);
+        }
+      }
+      vraw[i] = val;
+    }
+#pragma unroll
+    for (int j = 0; j < NU; ++j) {
+      const int e = j * NT + t;
+      const int pix = kbeg + kb * BK + (e >> 6), qg = q0 + (e & 63);
+      uraw[j] = (pix < kend && qg < prm.Q) ? __ldg(Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq) : 0.f;
+    }
+  };
+
+  auto store_tile = [&](int buf) {
+    uint32_t* vs = Vs + buf * BK * VS;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const float4 f = vraw[i];
+      uint4 wv;
+      wv.x = enc_v<EXACT>(__float_as_uint(f.x), prm.m);
+      wv.y = enc_v<EXACT>(__float_as_uint(f.y), prm.m);
+      wv.z = enc_v<EXACT>(__float_as_uint(f.z), prm.m);
+      wv.w = enc_v<EXACT>(__float_as_uint(f.w), prm.m);
+      *reinterpret_cast<uint4*>(vs + (i * RPP + krow0) * VS + pl) = wv;
+    }
+#pragma unroll
+    for (int j = 0; j < NU; ++j) {
+      const int e = j * NT + t;
+      store_u<EXACT>(UsP + buf * BK * BQ, UsR + buf * BK * BQ, UsE + buf * BK * BQ, e, __float_as_uint(uraw[j]), prm,
+                     lut_base);
+    }
+  };
+
+  float acc[TR][TC];
+#pragma unroll
+  for (int r = 0; r < TR; ++r)
+#pragma unroll
+    for (int c = 0; c < TC; ++c) acc[r][c] = 0.f;
+
+  const int nkb = (kend - kbeg + BK - 1) / BK;
+  const int vcol = wp * 128 + 4 * lane;
+  const int ucol = wq * TR;
+  if (nkb > 0) {
+    load_tile(0);
+    store_tile(0);
+  }
+  __syncthreads();
+  for (int kb = 0; kb < nkb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < nkb) load_tile(kb + 1);
+    const uint32_t* vs = Vs + buf * BK * VS + vcol;
+    const uint32_t* up = UsP + buf * BK * BQ + ucol;
+    const uint32_t* ur = UsR + buf * BK * BQ + ucol;
+    const uint32_t* ue = UsE + buf * BK * BQ + ucol;
+#pragma unroll 2
+    for (int kk = 0; kk < BK; ++kk)
+      mac_step<EXACT>(acc, vs + kk * VS, up + kk * BQ, ur + kk * BQ, ue + kk * BQ, prm.mult);
+    if (kb + 1 < nkb) store_tile(buf ^ 1);
+    __syncthreads();
+  }
+
+  float* __restrict__ Og = prm.splits > 1 ? prm.ws + (long long)blockIdx.z * ((long long)prm.P * prm.Q) : prm.O;
+  const bool vec_out = (prm.Q & 3) == 0 && ((reinterpret_cast<uintptr_t>(Og) & 15) == 0);
+#pragma unroll
+  for (int c = 0; c < TC; ++c) {
+    const int pg = p0 + vcol + c;
+    if (pg >= prm.P) continue;
+    float* orow = Og + (long long)pg * prm.Q;
+#pragma unroll
+    for (int g4 = 0; g4 < TR / 4; ++g4) {
+      const int qg = q0 + ucol + 4 * g4;
+      if (vec_out && qg + 3 < prm.Q) {
+        *reinterpret_cast<float4*>(orow + qg) =
+            make_float4(acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          if (qg + r < prm.Q) orow[qg + r] = acc[4 * g4 + r][c];
+      }
+    }
+  }
+}
+
+// Sums the split-K partials in ascending split order (fixed order: the result
+// does not depend on scheduling).
+__global__ void reduce_splits(const float* __restrict__ ws, float* __restrict__ out, long long n, int splits) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = ws[i];
+  for (int k = 1; k < splits; ++k) s = __fadd_rn(s, ws[(long long)k * n + i]);
+  out[i] = s;
+}
+
+// The reference primitive on raw LUT bytes (cuda/AMsimulator.inl:13-36).
+__device__ __forceinline__ uint32_t am_mul_bits(uint32_t at, uint32_t bt, const uint8_t* __restrict__ lut, int m) {
+  const uint32_t mask = ((1u << m) - 1u) << (23 - m);
+  const uint32_t idx = ((at & mask) >> (23 - 2 * m)) | ((bt & mask) >> (23 - m));
+  const uint32_t v = __ldg(lut + idx);
+  const uint32_t e = ((at >> 23) & 0xFFu) + ((bt >> 23) & 0xFFu);
+  if (e <= 127u) return 0u;
+  return ((at ^ bt) & 0x80000000u) + ((e - 127u + (v >> 7)) << 23) + ((v & 0x7Fu) << (23 - m));
+}
+
+__global__ void mul_elementwise(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                                size_t n, const uint8_t* __restrict__ lut, int m) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = __uint_as_float(am_mul_bits(__float_as_uint(a[i]), __float_as_uint(b[i]), lut, m));
+}
+
+}  // namespace amsim

@@ -1,0 +1,169 @@
+/*
+ * amsim — C ABI of the B200 (sm_100a) AM-Simulator kernels.
+ *
+ * Drop-in boundary for ApproxTrain's GPU functors: each entry point below
+ * replaces one functor that the reference's TensorFlow op hosts call
+ * (convam.h / denseam.h / matmulam.h / approx_mul_lut.h), with the same
+ * argument meaning.  Differences that hold for every call:
+ *
+ *   - plain C types only; all tensor pointers are DEVICE pointers to FP32
+ *     data owned by the caller (NHWC activations, HWIO filters, row-major
+ *     matrices), the LUT handle owns its own device memory;
+ *   - `stream` is a cudaStream_t passed as void*; calls are stream-ordered,
+ *     never synchronise the device and never exit the process (the reference
+ *     calls cudaDeviceSynchronize after every launch and exit(1) on error,
+ *     cuda/error.cuh:11-27);
+ *   - the return value is an AMSIM_* status; amsim_last_error() gives the text
+ *     of the calling thread's last failure;
+ *   - no im2col or reversed-filter scratch is needed (convam.h:69-105 take
+ *     `im2col` and `rsfilter` buffers): the gathers are index maps inside the
+ *     kernels.  Only the split-K gradient kernels use caller-provided scratch.
+ *
+ * `flags`:
+ *   AMSIM_FAST           default.  Products equal the reference primitive
+ *                        except where an operand has a zero exponent field
+ *                        (product taken as 0) or the exponent sum is <= 127
+ *                        (reference returns 0, here the exact tiny product,
+ *                        < 2^-125); each forward / input-gradient output is one
+ *                        ascending-k FP32 chain like the reference kernel, the
+ *                        filter / weight gradients are split along the
+ *                        reduction and summed in a fixed order.
+ *   AMSIM_DETERMINISTIC  every product is the reference primitive bit for bit
+ *                        (cuda/AMsimulator.inl:13-36) and every output is one
+ *                        ascending chain in the reference's order
+ *                        (cuda/gemm.cu:30-53): results are bit-identical to the
+ *                        reference GPU kernels.  Slower.
+ */
+#ifndef AMSIM_H_
+#define AMSIM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AMSIM_OK 0
+#define AMSIM_ERR_INVALID 1      /* null pointer, bad shape, bad flag */
+#define AMSIM_ERR_LUT_NAME 2     /* mantissa width not parseable / out of 1..11 */
+#define AMSIM_ERR_LUT_IO 3       /* file cannot be opened or read */
+#define AMSIM_ERR_LUT_SIZE 4     /* file is not exactly 2^(2m) bytes */
+#define AMSIM_ERR_CUDA 5         /* a CUDA runtime call failed */
+#define AMSIM_ERR_WORKSPACE 6    /* scratch buffer missing or too small */
+#define AMSIM_ERR_UNSUPPORTED 7  /* valid request this build cannot serve */
+
+#define AMSIM_FAST 0u
+#define AMSIM_DETERMINISTIC 1u
+
+typedef struct amsim_lut amsim_lut; /* opaque, immutable after open */
+
+/* Text of the calling thread's most recent failure ("" if none). */
+const char* amsim_last_error(void);
+
+/* Library version string and the SM architecture the kernels were built for. */
+const char* amsim_version(void);
+
+/* ---- LUT ------------------------------------------------------------------
+ * Replaces approx_mul_lut_base::load_lut_binary (approx_mul_lut.h:15-45) and
+ * approx_mul_lut<GpuDevice> (cuda/approx_mul_lut.cu:24-53).  `path` is the
+ * op's `mant_mul_lut` attribute: "<MODEL>_<m>.bin", m = digits between the
+ * last '_' and the last '.', file = 2^(2m) raw bytes.  Handles are cached per
+ * (real path, device) and reference counted; close drops one reference.
+ * The file must hold exactly 2^(2m) bytes (the reference reads "up to"). */
+int amsim_lut_open(const char* path, int device, amsim_lut** out);
+/* Same, from bytes already in host memory (m given explicitly). */
+int amsim_lut_open_bytes(const uint8_t* bytes, int m, int device, amsim_lut** out);
+int amsim_lut_close(amsim_lut* lut);
+/* approx_mul_lut.h:53-70 getters: mantissa width, mask, shifts; the raw LUT
+ * bytes on the device (what the reference binds to its texture object). */
+int amsim_lut_info(const amsim_lut* lut, int* mant_width, uint32_t* mant_mask,
+                   int* a_shift, int* b_shift, const uint8_t** device_bytes);
+
+/* ---- the primitive ----------------------------------------------------------
+ * out[i] = AMsimulator(a[i], b[i]) — cuda/AMsimulator.inl:13-36, bit-exact,
+ * every m in 1..11.  The reference has no elementwise op; this exposes the
+ * primitive the GEMM kernels are built on so it can be checked on its own. */
+int amsim_mul(void* stream, const amsim_lut* lut, const float* a, const float* b,
+              float* out, size_t n);
+
+/* ---- convolution geometry -----------------------------------------------------
+ * TF window arithmetic used by ConvamOp::Compute (convam.cc:315-407) and the
+ * filter_left/top_offset derivation (convam.cc:557-572): same != 0 -> SAME.
+ * pad_top / pad_left are the forward pad-before amounts (0 for VALID). */
+int amsim_conv2d_geometry(int in_h, int in_w, int f_h, int f_w, int stride_h,
+                          int stride_w, int same, int* out_h, int* out_w,
+                          int* pad_top, int* pad_left);
+
+/* ---- AMConv2D -------------------------------------------------------------------
+ * Forward: replaces ConvamFunctor<GPUDevice> (convam.h:69-80,
+ * cuda/cuda_kernel.cu:100-321).  y[n,oh,ow,k] = sum over (kh,kw,c) of
+ * AM(x[n, oh*sh - pad_top + kh, ow*sw - pad_left + kw, c] or 0, w[kh,kw,c,k]). */
+int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x,
+                     const float* w, float* y, int batch, int in_h, int in_w,
+                     int in_c, int f_h, int f_w, int out_c, int out_h, int out_w,
+                     int stride_h, int stride_w, int pad_top, int pad_left,
+                     unsigned flags);
+
+/* Input gradient: replaces ConvamInputGradFunctor<GPUDevice> (convam.h:82-93,
+ * cuda/cuda_kernel.cu:462-657) including cuda/reverseNswapdim23.cu.  The
+ * functor's hole_grad_* and back-pad arguments are derived here from the
+ * forward geometry (convam.cc:1066-1084). */
+int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w,
+                           const float* dy, float* dx, int batch, int in_h,
+                           int in_w, int in_c, int f_h, int f_w, int out_c,
+                           int out_h, int out_w, int stride_h, int stride_w,
+                           int pad_top, int pad_left, unsigned flags);
+
+/* Filter gradient: replaces ConvamFilterGradFunctor<GPUDevice>
+ * (convam.h:95-105, cuda/cuda_kernel.cu:326-461).  AMSIM_FAST splits the
+ * N*OH*OW reduction over thread blocks and needs `workspace` of at least
+ * amsim_conv2d_bwd_filter_workspace(...) bytes (device memory, 256-byte
+ * aligned, contents irrelevant on entry, clobbered on return; 0 bytes means
+ * none needed and NULL is accepted). */
+size_t amsim_conv2d_bwd_filter_workspace(int batch, int in_h, int in_w, int in_c,
+                                         int f_h, int f_w, int out_c, int out_h,
+                                         int out_w, unsigned flags);
+int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x,
+                            const float* dy, float* dw, int batch, int in_h,
+                            int in_w, int in_c, int f_h, int f_w, int out_c,
+                            int out_h, int out_w, int stride_h, int stride_w,
+                            int pad_top, int pad_left, void* workspace,
+                            size_t workspace_bytes, unsigned flags);
+
+/* ---- denseam ---------------------------------------------------------------------
+ * Replace DenseamFunctor / DenseamWeightGradFunctor / DenseamInputGradFunctor
+ * (denseam.h:7-28, cuda/denseam_kernel.cu:18-145).  x[batch,input_width],
+ * w[input_width,units], y and g [batch,units], all row-major. */
+int amsim_dense_fwd(void* stream, const amsim_lut* lut, const float* x,
+                    const float* w, float* y, int batch, int units,
+                    int input_width, unsigned flags);
+size_t amsim_dense_bwd_weight_workspace(int batch, int units, int input_width,
+                                        unsigned flags);
+int amsim_dense_bwd_weight(void* stream, const amsim_lut* lut, const float* x,
+                           const float* g, float* dw, int batch, int units,
+                           int input_width, void* workspace,
+                           size_t workspace_bytes, unsigned flags);
+int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w,
+                          const float* g, float* dx, int batch, int units,
+                          int input_width, unsigned flags);
+
+/* ---- MatMulAM ----------------------------------------------------------------------
+ * Replaces LaunchMatMul<GpuDevice> (matmulam.h:10-18,
+ * cuda/matmulam_kernel.cu:11-99) with one launch for all batches.
+ * batch_* == 0 means the operand is rank 2; batch 1 broadcasts; when both are
+ * > 1 they must be equal (matmulam.cc:93).  col_a must equal row_b.  Output is
+ * [max(batch_a,batch_b,1)] x row_a x col_b.  Every output batch is computed
+ * (the reference computes only the first when batch_a == 1 < batch_b). */
+int amsim_matmul(void* stream, const amsim_lut* lut, const float* a,
+                 const float* b, float* c, int batch_a, int batch_b, int row_a,
+                 int col_a, int row_b, int col_b, unsigned flags);
+
+/* Host-side check of the kernels' constant-divisor arithmetic (no GPU work):
+ * returns n / d computed the way the device code does.  For tests. */
+uint32_t amsim_debug_fastdiv(uint32_t n, uint32_t d);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AMSIM_H_ */
