@@ -37,7 +37,6 @@ int fail(int code, const char* fmt, ...) {
     if (e_ != cudaSuccess) return fail(AMSIM_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
   } while (0)
 
-constexpr int kTargetCtas = 2 * 148;  // two resident CTAs on each of the 148 SMs
 
 }  // namespace
 
@@ -96,7 +95,7 @@ int upload_lut(const uint8_t* bytes, int m, int device, amsim_lut** out) {
     if (e != cudaSuccess) bail(e, "cudaMemcpy(lut)");
   }
   if (rc == AMSIM_OK && m <= 7) {
-    const int side = 1 << m, stride = side + 4;
+    const int side = 1 << m, stride = side;
     h->enc_bytes = (side * stride + 15) / 16 * 16;
     std::vector<uint8_t> canon(h->enc_bytes, 0), trans(h->enc_bytes, 0);
     for (int a = 0; a < side; ++a)
@@ -155,7 +154,11 @@ void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
   p.lut_bytes = lut->enc_bytes;
   p.m = lut->m;
   p.mult = 1u << (23 - lut->m);
-  p.rowstride = (1u << lut->m) + 4u;
+  p.rowstride = 1u << lut->m;
+  p.rmask = ((1u << lut->m) - 1u) << lut->m;
+  uint32_t al = 16;
+  while (al < (uint32_t)lut->enc_bytes) al <<= 1;
+  p.lut_align = al;
 }
 
 void fill_gather_divs(Gather& g) {
@@ -171,8 +174,8 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <int WP, bool EXACT, bool VEC>
 int launch_gather_t(cudaStream_t st, const Params& p, int batch, int device) {
-  using L = SmemLayout<WP, EXACT>;
-  const size_t smem = L::bytes(p.lut_bytes);
+  using L = SmemLayout<WP>;
+  const size_t smem = L::bytes(p.lut_bytes, p.lut_align);
   int rc = ensure_smem(gather_gemm<WP, EXACT, VEC>, smem, device);
   if (rc) return rc;
   dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, batch);
@@ -185,8 +188,12 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
   if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
   if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
-  const long long ctas2 = (long long)((p.P + 255) / 256) * ((p.Q + BQ - 1) / BQ) * batch;
-  const bool wide = ctas2 >= 148;
+  // Tile height: the one that leaves the busiest SM with fewer rows to process.
+  const long long qb = (long long)((p.Q + BQ - 1) / BQ) * batch;
+  const long long rows1 = (((long long)((p.P + 127) / 128) * qb + 147) / 148) * 128;
+  const long long rows2 = (((long long)((p.P + 255) / 256) * qb + 147) / 148) * 256;
+  bool wide = rows2 < rows1;
+  if (const char* f = getenv("AMSIM_FORCE_WP")) wide = atoi(f) == 2;
 #define AMSIM_GO(WP_, EX_, VEC_) return launch_gather_t<WP_, EX_, VEC_>(st, p, batch, device)
   if (wide) {
     if (exact) { if (vec) AMSIM_GO(2, true, true); else AMSIM_GO(2, true, false); }
@@ -205,14 +212,15 @@ struct FgradPlan {
 
 FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
   FgradPlan f;
-  const double waste1 = (double)((P + 127) / 128) * 128 / (P > 0 ? P : 1);
-  const double waste2 = (double)((P + 255) / 256) * 256 / (P > 0 ? P : 1);
-  f.wp = (waste2 <= waste1 + 0.02) ? 2 : 1;
+  f.wp = 1;  // 128-row tiles: 3 CTAs of 4 warps per SM without register spills
+  if (const char* e = getenv("AMSIM_FORCE_WP")) f.wp = atoi(e) == 2 ? 2 : 1;
   const int bp = f.wp * 128;
+  const int slots = 148 * (f.wp == 1 ? 3 : 2);  // resident CTAs on the whole GPU
   const long long tiles = (long long)((P + bp - 1) / bp) * ((Q + BQ - 1) / BQ);
   int splits = 1;
   if (!exact && tiles > 0) {
-    splits = (int)((kTargetCtas + tiles - 1) / tiles);
+    // one balanced wave: as many splits as fit in the resident slots
+    splits = (int)(slots / tiles);
     const int max_splits = (K + 4 * BK - 1) / (4 * BK);  // at least 4 stages per split
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
@@ -228,8 +236,8 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
 
 template <int WP, bool EXACT, bool VEC>
 int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
-  using L = SmemLayout<WP, EXACT>;
-  const size_t smem = L::bytes(p.lut_bytes);
+  using L = SmemLayout<WP>;
+  const size_t smem = L::bytes(p.lut_bytes, p.lut_align);
   int rc = ensure_smem(fgrad_gemm<WP, EXACT, VEC>, smem, device);
   if (rc) return rc;
   dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, p.splits);

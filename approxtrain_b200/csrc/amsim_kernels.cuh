@@ -14,16 +14,21 @@
 //
 // Why this shape.  Each product needs one byte from a 2^m x 2^m table.  The
 // table sits in shared memory with one row per value of the WARP-UNIFORM
-// operand (row = 2^m bytes + a zero column, at most 132 bytes), so the 32 byte
-// reads of one LDS all fall into a single 128-byte-wide bank row (plus at most
-// one wrap-around word) and are served in one wavefront: the table lookup is
-// conflict free by construction, whatever the data.  The inner loop per product
-// is: address add, LDS.U8, integer multiply-add that rebuilds the product's
-// significand/exponent bits next to the lane operand's sign+exponent, and one
-// FFMA with the uniform operand's power of two (the product of a float and a
-// power of two is exact, so the FFMA rounds exactly like the reference's
-// "accumulator + product" add).  Tensor cores cannot be used: no product is a
-// hardware multiply.
+// operand (row = 2^m bytes, at most 128 = one word per bank), so the 32 byte
+// reads of one LDS all fall into a single bank row and are served in one
+// wavefront: the table lookup is conflict free by construction, whatever the
+// data.  The table is placed at a shared-memory address aligned to its size,
+// so "row bits | column bits | base" is a pure OR.  The inner loop per product
+// is: one 3-input logic op forming the address, LDS.U8, an integer
+// multiply-add that rebuilds the product's significand/exponent bits next to
+// the lane operand's sign+exponent, and one FFMA with the uniform operand's
+// power of two (the product of a float and a power of two is exact, so the
+// FFMA rounds exactly like the reference's "accumulator + product" add).
+// What bounds it: each lookup returns 4 bytes per lane through the 128-byte/clk
+// shared-memory return path, i.e. 32 products per clock per SM at most; the
+// operand words fetched from shared memory share that path, which is why the
+// uniform operand is packed into ONE word per element.  Tensor cores cannot be
+// used: no product is a hardware multiply.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -34,6 +39,13 @@ constexpr int BK = 16;  // reduction steps per shared-memory stage
 constexpr int BQ = 64;  // q extent of a CTA tile (4 warps x 16)
 constexpr int TR = 16;  // q values per warp, held as registers
 constexpr int TC = 4;   // consecutive p values per lane
+
+#ifndef AMSIM_KUNROLL
+#define AMSIM_KUNROLL 1
+#endif
+#define AMSIM_STR2(x) #x
+#define AMSIM_STR(x) AMSIM_STR2(x)
+#define AMSIM_UNROLL_K _Pragma(AMSIM_STR(unroll AMSIM_KUNROLL))
 
 // Division by a run-time constant: n / d for n < 2^31.
 struct FastDiv {
@@ -97,7 +109,9 @@ struct Params {
   int lut_bytes;                // multiple of 16
   int m;
   uint32_t mult;                // 1 << (23 - m)
-  uint32_t rowstride;           // (1 << m) + 4
+  uint32_t rowstride;           // 1 << m
+  uint32_t rmask;               // ((1 << m) - 1) << m : row bits of a table address
+  uint32_t lut_align;           // power of two >= lut_bytes: alignment of the table in shared memory
   // fgrad only
   int k_chunk, splits;
   float* ws;                    // [splits][P][Q] partial sums when splits > 1
@@ -115,8 +129,8 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) {
 
 // ---- operand encodings -------------------------------------------------------
 // Lane operand (V): one word = sign+exponent bits | table column.
-//   fast:  a zero exponent field selects the all-zero table column and drops
-//          the sign/exponent, so the rebuilt factor is exactly 0.
+//   fast:  a zero exponent field (zero or denormal) becomes the word 0, which
+//          the inner loop predicates off: the product is exactly 0.
 //   exact: the raw fields, nothing special-cased (the reference pushes zeros
 //          and denormals through the table like any other value).
 template <bool EXACT>
@@ -124,26 +138,26 @@ __device__ __forceinline__ uint32_t enc_v(uint32_t bits, int m) {
   const uint32_t idx = (bits >> (23 - m)) & ((1u << m) - 1u);
   const uint32_t w = (bits & 0xFF800000u) | idx;
   if (EXACT) return w;
-  return (bits & 0x7F800000u) ? w : (1u << m);
+  return (bits & 0x7F800000u) ? w : 0u;
 }
 
 // One reduction step of a 16 (q) x 4 (p) register tile.
-//   vrow : 4 consecutive lane-operand words
-//   uP   : 16 uniform-operand sign+exponent words (as floats: +-2^(e-127))
-//   uR   : 16 shared-memory byte addresses of the uniform operand's table row
-//   uE   : exact mode only, 16 exponent fields (e << 23)
+//   vrow : 4 consecutive lane-operand words (sign+exponent | column)
+//   urow : 16 uniform-operand words (sign+exponent | column << m)
+//   lut_base : shared-memory address of the table (aligned to its size)
 template <bool EXACT>
 __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* __restrict__ vrow,
-                                         const uint32_t* __restrict__ uP,
-                                         const uint32_t* __restrict__ uR,
-                                         const uint32_t* __restrict__ uE, const uint32_t mult) {
+                                         const uint32_t* __restrict__ urow, const uint32_t lut_base,
+                                         const uint32_t rmask, const uint32_t mult) {
   const uint4 cw = *reinterpret_cast<const uint4*>(vrow);
   const uint32_t w[TC] = {cw.x, cw.y, cw.z, cw.w};
   uint32_t ci[TC], cs[TC];
   int cn[TC];
+  bool nz[TC];
 #pragma unroll
   for (int t = 0; t < TC; ++t) {
-    ci[t] = w[t] & 0x1FFu;
+    ci[t] = (w[t] & 0xFFu) | lut_base;
+    nz[t] = w[t] != 0u;
     if (EXACT) {
       // AMsimulator.inl:26-33: exponent sum - 127, folded into the lane word
       cs[t] = (w[t] & 0xFF800000u) - 0x3F800000u;
@@ -154,29 +168,25 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
   }
 #pragma unroll
   for (int g4 = 0; g4 < TR / 4; ++g4) {
-    const uint4 p4 = *reinterpret_cast<const uint4*>(uP + 4 * g4);
-    const uint4 r4 = *reinterpret_cast<const uint4*>(uR + 4 * g4);
-    const uint32_t pp[4] = {p4.x, p4.y, p4.z, p4.w};
-    const uint32_t rr[4] = {r4.x, r4.y, r4.z, r4.w};
-    uint32_t ee[4] = {0, 0, 0, 0};
-    if (EXACT) {
-      const uint4 e4 = *reinterpret_cast<const uint4*>(uE + 4 * g4);
-      ee[0] = e4.x; ee[1] = e4.y; ee[2] = e4.z; ee[3] = e4.w;
-    }
+    const uint4 u4 = *reinterpret_cast<const uint4*>(urow + 4 * g4);
+    const uint32_t uu[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
+      const uint32_t pp = uu[r] & 0xFF800000u;
+      const int ee = (int)(uu[r] & 0x7F800000u);
 #pragma unroll
       for (int t = 0; t < TC; ++t) {
-        const uint32_t v = lds_u8(rr[r] + ci[t]);
+        const uint32_t v = lds_u8((uu[r] & rmask) | ci[t]);
         if (EXACT) {
           // bits = sign + ((ea + eb - 127 + carry) << 23) + mantissa, uint32 wrap
-          const uint32_t bits = v * mult + (pp[r] + cs[t]);
+          const uint32_t bits = v * mult + (pp + cs[t]);
           // product is +0 when ea + eb <= 127 (AMsimulator.inl:28); adding +0
           // never changes a non-negative-zero accumulator, so skip the add.
-          if ((int)ee[r] > cn[t]) acc[4 * g4 + r][t] = __fadd_rn(acc[4 * g4 + r][t], __uint_as_float(bits));
+          if (ee > cn[t]) acc[4 * g4 + r][t] = __fadd_rn(acc[4 * g4 + r][t], __uint_as_float(bits));
         } else {
           const float y = __uint_as_float(v * mult + cs[t]);
-          acc[4 * g4 + r][t] = __fmaf_rn(__uint_as_float(pp[r]), y, acc[4 * g4 + r][t]);
+          const float sacc = __fmaf_rn(__uint_as_float(pp), y, acc[4 * g4 + r][t]);
+          acc[4 * g4 + r][t] = nz[t] ? sacc : acc[4 * g4 + r][t];
         }
       }
     }
@@ -190,25 +200,21 @@ __device__ __forceinline__ void copy_lut_to_smem(uint8_t* lut_s, const uint8_t* 
   for (int i = tid; i < bytes / 16; i += nthreads) dst[i] = __ldg(src + i);
 }
 
-// Stores the uniform-operand (U) words of one element.
-template <bool EXACT>
-__device__ __forceinline__ void store_u(uint32_t* uP, uint32_t* uR, uint32_t* uE, int at, uint32_t bits,
-                                        const Params& prm, uint32_t lut_base) {
-  const uint32_t idx = (bits >> (23 - prm.m)) & ((1u << prm.m) - 1u);
-  uP[at] = bits & 0xFF800000u;
-  uR[at] = lut_base + idx * prm.rowstride;
-  if (EXACT) uE[at] = bits & 0x7F800000u;
+// Uniform operand (U): one word = sign+exponent bits | table row bits.
+__device__ __forceinline__ uint32_t enc_u(uint32_t bits, int m) {
+  return (bits & 0xFF800000u) | (((bits >> (23 - m)) & ((1u << m) - 1u)) << m);
 }
 
-template <int WP, bool EXACT>
+template <int WP>
 struct SmemLayout {
   static constexpr int NT = WP * 128;
   static constexpr int BP = WP * 128;
   static constexpr int VS = BP + 4;  // padded row: conflict-free 4-row scatter
   static constexpr int V_WORDS = 2 * BK * VS;
   static constexpr int U_WORDS = 2 * BK * BQ;
-  static constexpr int WORDS = V_WORDS + U_WORDS * (EXACT ? 3 : 2);
-  static size_t bytes(int lut_bytes) { return (size_t)lut_bytes + (size_t)WORDS * 4; }
+  static constexpr int TILE_BYTES = (V_WORDS + U_WORDS) * 4;
+  // tiles, then the table at the next multiple of its alignment
+  static size_t bytes(int lut_bytes, int lut_align) { return (size_t)TILE_BYTES + lut_align + lut_bytes; }
 };
 
 // -----------------------------------------------------------------------------
@@ -216,16 +222,16 @@ struct SmemLayout {
 // -----------------------------------------------------------------------------
 template <int WP, bool EXACT, bool VEC>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) gather_gemm(const Params prm) {
-  using L = SmemLayout<WP, EXACT>;
+  using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
   constexpr int NU = BK * BQ / NT;  // U elements staged per thread
 
   extern __shared__ __align__(16) uint8_t smem[];
-  uint8_t* lut_s = smem;
-  uint32_t* Vs = reinterpret_cast<uint32_t*>(smem + prm.lut_bytes);
-  uint32_t* UsP = Vs + L::V_WORDS;
-  uint32_t* UsR = UsP + L::U_WORDS;
-  uint32_t* UsE = UsR + L::U_WORDS;
+  uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);
+  uint32_t* Us = Vs + L::V_WORDS;
+  const uint32_t smem_base = smem_addr(smem);
+  const uint32_t lut_base = (smem_base + L::TILE_BYTES + prm.lut_align - 1) & ~(prm.lut_align - 1);
+  uint8_t* lut_s = smem + (lut_base - smem_base);
 
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
   const int wp = w % WP, wq = w / WP;
@@ -236,7 +242,6 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) gather_gemm(const P
   const Gather& g = prm.g;
 
   copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
-  const uint32_t lut_base = smem_addr(lut_s);
 
   // ---- this thread's share of the V tile: 2 rows (p) x 2 groups of 4 k ------
   int pl[2], r0[2], c0[2];
@@ -337,8 +342,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) gather_gemm(const P
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
-      store_u<EXACT>(UsP + buf * BK * BQ, UsR + buf * BK * BQ, UsE + buf * BK * BQ, e, __float_as_uint(uraw[j]), prm,
-                     lut_base);
+      Us[buf * BK * BQ + e] = enc_u(__float_as_uint(uraw[j]), prm.m);
     }
   };
 
@@ -359,12 +363,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) gather_gemm(const P
     const int buf = kb & 1;
     if (kb + 1 < nkb) load_tile(kb + 1);
     const uint32_t* vs = Vs + buf * BK * VS + vcol;
-    const uint32_t* up = UsP + buf * BK * BQ + ucol;
-    const uint32_t* ur = UsR + buf * BK * BQ + ucol;
-    const uint32_t* ue = UsE + buf * BK * BQ + ucol;
-#pragma unroll 2
+    const uint32_t* us = Us + buf * BK * BQ + ucol;
+AMSIM_UNROLL_K
     for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT>(acc, vs + kk * VS, up + kk * BQ, ur + kk * BQ, ue + kk * BQ, prm.mult);
+      mac_step<EXACT>(acc, vs + kk * VS, us + kk * BQ, lut_base, prm.rmask, prm.mult);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }
@@ -401,7 +403,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) gather_gemm(const P
 // -----------------------------------------------------------------------------
 template <int WP, bool EXACT, bool VEC>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) fgrad_gemm(const Params prm) {
-  using L = SmemLayout<WP, EXACT>;
+  using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
   constexpr int NU = BK * BQ / NT;
   constexpr int GPR = BP / 4;        // 4-wide p groups per k row
@@ -409,11 +411,11 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) fgrad_gemm(const Pa
   constexpr int NV = BK / RPP;       // passes (= 4)
 
   extern __shared__ __align__(16) uint8_t smem[];
-  uint8_t* lut_s = smem;
-  uint32_t* Vs = reinterpret_cast<uint32_t*>(smem + prm.lut_bytes);
-  uint32_t* UsP = Vs + L::V_WORDS;
-  uint32_t* UsR = UsP + L::U_WORDS;
-  uint32_t* UsE = UsR + L::U_WORDS;
+  uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);
+  uint32_t* Us = Vs + L::V_WORDS;
+  const uint32_t smem_base = smem_addr(smem);
+  const uint32_t lut_base = (smem_base + L::TILE_BYTES + prm.lut_align - 1) & ~(prm.lut_align - 1);
+  uint8_t* lut_s = smem + (lut_base - smem_base);
 
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
   const int wp = w % WP, wq = w / WP;
@@ -425,7 +427,6 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) fgrad_gemm(const Pa
   const float* __restrict__ Ug = prm.U;
 
   copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
-  const uint32_t lut_base = smem_addr(lut_s);
 
   // ---- this thread's 4 consecutive p (same for every k row it stages) ---------
   const int pl = 4 * (t % GPR);
@@ -498,8 +499,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) fgrad_gemm(const Pa
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
-      store_u<EXACT>(UsP + buf * BK * BQ, UsR + buf * BK * BQ, UsE + buf * BK * BQ, e, __float_as_uint(uraw[j]), prm,
-                     lut_base);
+      Us[buf * BK * BQ + e] = enc_u(__float_as_uint(uraw[j]), prm.m);
     }
   };
 
@@ -521,12 +521,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) fgrad_gemm(const Pa
     const int buf = kb & 1;
     if (kb + 1 < nkb) load_tile(kb + 1);
     const uint32_t* vs = Vs + buf * BK * VS + vcol;
-    const uint32_t* up = UsP + buf * BK * BQ + ucol;
-    const uint32_t* ur = UsR + buf * BK * BQ + ucol;
-    const uint32_t* ue = UsE + buf * BK * BQ + ucol;
-#pragma unroll 2
+    const uint32_t* us = Us + buf * BK * BQ + ucol;
+AMSIM_UNROLL_K
     for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT>(acc, vs + kk * VS, up + kk * BQ, ur + kk * BQ, ue + kk * BQ, prm.mult);
+      mac_step<EXACT>(acc, vs + kk * VS, us + kk * BQ, lut_base, prm.rmask, prm.mult);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }
