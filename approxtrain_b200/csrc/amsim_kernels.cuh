@@ -40,6 +40,9 @@ constexpr int BQ = 64;  // q extent of a CTA tile (4 warps x 16)
 constexpr int TR = 16;  // q values per warp, held as registers
 constexpr int TC = 4;   // consecutive p values per lane
 
+#ifndef AMSIM_CTAS1
+#define AMSIM_CTAS1 3
+#endif
 #ifndef AMSIM_KUNROLL
 #define AMSIM_KUNROLL 1
 #endif
@@ -221,7 +224,7 @@ struct SmemLayout {
 // gather_gemm: V gathered along k.  grid = (ceil(P/BP), ceil(Q/64), batch).
 // -----------------------------------------------------------------------------
 template <int WP, bool EXACT, bool VEC>
-__global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) gather_gemm(const Params prm) {
+__global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
   constexpr int NU = BK * BQ / NT;  // U elements staged per thread
@@ -402,7 +405,7 @@ AMSIM_UNROLL_K
 // is only one split).
 // -----------------------------------------------------------------------------
 template <int WP, bool EXACT, bool VEC>
-__global__ void __launch_bounds__(WP * 128, WP == 1 ? 3 : 2) fgrad_gemm(const Params prm) {
+__global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
   constexpr int NU = BK * BQ / NT;
