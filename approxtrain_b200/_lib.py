@@ -14,12 +14,14 @@ OK = 0
 ERR_INVALID, ERR_LUT_NAME, ERR_LUT_IO, ERR_LUT_SIZE, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED = range(1, 8)
 FAST = 0
 DETERMINISTIC = 1
+STATIC_SCRATCH_BYTES = 8 << 20
 
 # every symbol include/amsim.h declares
 EXPORTS = [
     "amsim_last_error", "amsim_version", "amsim_lut_open", "amsim_lut_open_bytes", "amsim_lut_close",
     "amsim_lut_info", "amsim_mul", "amsim_conv2d_geometry", "amsim_conv2d_fwd", "amsim_conv2d_bwd_input",
-    "amsim_conv2d_bwd_filter_workspace", "amsim_conv2d_bwd_filter", "amsim_dense_fwd",
+    "amsim_conv2d_bwd_filter_workspace", "amsim_conv2d_bwd_filter", "amsim_conv2d_bwd_filter_static",
+    "amsim_dense_fwd",
     "amsim_dense_bwd_weight_workspace", "amsim_dense_bwd_weight", "amsim_dense_bwd_input", "amsim_matmul",
     "amsim_debug_fastdiv",
 ]
@@ -53,6 +55,7 @@ def _load() -> C.CDLL:
     L.amsim_conv2d_bwd_filter_workspace.argtypes = [ip] * 9 + [u]
     L.amsim_conv2d_bwd_filter_workspace.restype = sz
     L.amsim_conv2d_bwd_filter.argtypes = [vp, vp, fp, fp, fp] + conv_dims + [vp, sz, u]
+    L.amsim_conv2d_bwd_filter_static.argtypes = [vp, vp, fp, fp, fp] + conv_dims + [u]
     L.amsim_dense_fwd.argtypes = [vp, vp, fp, fp, fp, ip, ip, ip, u]
     L.amsim_dense_bwd_weight_workspace.argtypes = [ip, ip, ip, u]
     L.amsim_dense_bwd_weight_workspace.restype = sz

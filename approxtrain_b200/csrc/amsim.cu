@@ -483,6 +483,48 @@ int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, 
   return launch_fgrad((cudaStream_t)stream, p, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
 }
 
+// ---- built-in scratch for amsim_conv2d_bwd_filter_static ----------------------
+// Lives in the device image of this library; in host code the symbol's name is
+// only a handle, the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[AMSIM_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the CURRENT device, looked up once per
+// device (the first call on a device does the lookup).
+static int static_scratch_address(int device, void** out) {
+  static std::mutex mu;
+  static std::map<int, void*> known;
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = known.find(device);
+  if (it != known.end()) {
+    *out = it->second;
+    return AMSIM_OK;
+  }
+  void* p = nullptr;
+  CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+  if (!p) return fail(AMSIM_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the built-in scratch");
+  known[device] = p;
+  *out = p;
+  return AMSIM_OK;
+}
+
+int amsim_conv2d_bwd_filter_static(void* stream, const amsim_lut* lut, const float* x, const float* dy, float* dw,
+                                   int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
+                                   int out_w, int stride_h, int stride_w, int pad_top, int pad_left, unsigned flags) {
+  int rc = check_common(lut, flags, true);  // also checks that lut->device is the current device
+  if (rc) return rc;
+  const size_t need =
+      amsim_conv2d_bwd_filter_workspace(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, flags);
+  if (need > (size_t)AMSIM_STATIC_SCRATCH_BYTES)
+    return fail(AMSIM_ERR_WORKSPACE,
+                "this shape needs %zu bytes of split-K scratch, the built-in buffer holds %u: "
+                "use amsim_conv2d_bwd_filter with a caller-provided workspace",
+                need, (unsigned)AMSIM_STATIC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  if (need > 0 && (rc = static_scratch_address(lut->device, &scratch))) return rc;
+  return amsim_conv2d_bwd_filter(stream, lut, x, dy, dw, batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w,
+                                 stride_h, stride_w, pad_top, pad_left, scratch, need, flags);
+}
+
 static void dense_gather(Gather& g, int width) {
   g.PH = 1; g.PW = 1; g.ps_h = 1; g.ps_w = 1; g.off_t = 0; g.off_l = 0; g.lim_h = 1; g.lim_w = 1;
   g.dil_h = 1; g.dil_w = 1; g.SH = 1; g.SW = 1; g.SC = width; g.KW = 1;

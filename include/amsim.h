@@ -131,6 +131,38 @@ int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x,
                             int pad_top, int pad_left, void* workspace,
                             size_t workspace_bytes, unsigned flags);
 
+/* Filter gradient for callers that cannot hand over scratch memory.
+ * (No counterpart in the reference: its functor takes the scratch from the
+ * TensorFlow allocator.)
+ *
+ * Same computation, same split plan and therefore bit-identical results as
+ * amsim_conv2d_bwd_filter, but the split-K partial sums live in a buffer that
+ * is part of the library image on the device (AMSIM_STATIC_SCRATCH_BYTES,
+ * resident on every GPU that loads the library until the process exits)
+ * instead of a caller-supplied workspace.  It is meant for hosts that have no
+ * way to allocate at the point of the call: a plain C driver without a device
+ * allocator, an op host whose framework offers no temporary tensors there, or
+ * stream-ordered code that must not call cudaMalloc because that call
+ * synchronises the whole device.  The call itself performs no cudaMalloc /
+ * cudaFree and calls nothing that allocates device memory.
+ *
+ *  - A shape whose plan needs more than AMSIM_STATIC_SCRATCH_BYTES is refused
+ *    with AMSIM_ERR_WORKSPACE (nothing is launched); use the workspace variant.
+ *  - The first call on a device looks up the buffer's device address
+ *    (cudaGetSymbolAddress); make that first call before starting any stream
+ *    capture on that device.
+ *  - The buffer is shared by every call in the process and keeps whatever the
+ *    previous call left in it.  Nothing in it has to start at zero: every
+ *    partial sum a call reads back was written by that same call.  Two calls
+ *    that may run at the same time on one GPU (different streams or threads)
+ *    would overwrite each other's partial sums: serialise them. */
+#define AMSIM_STATIC_SCRATCH_BYTES (8u << 20)
+int amsim_conv2d_bwd_filter_static(void* stream, const amsim_lut* lut, const float* x,
+                                   const float* dy, float* dw, int batch, int in_h,
+                                   int in_w, int in_c, int f_h, int f_w, int out_c,
+                                   int out_h, int out_w, int stride_h, int stride_w,
+                                   int pad_top, int pad_left, unsigned flags);
+
 /* ---- denseam ---------------------------------------------------------------------
  * Replace DenseamFunctor / DenseamWeightGradFunctor / DenseamInputGradFunctor
  * (denseam.h:7-28, cuda/denseam_kernel.cu:18-145).  x[batch,input_width],
