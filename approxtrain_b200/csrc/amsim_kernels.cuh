@@ -39,6 +39,7 @@ constexpr int BK = 16;  // reduction steps per shared-memory stage
 constexpr int BQ = 64;  // q extent of a CTA tile (4 warps x 16)
 constexpr int TR = 16;  // q values per warp, held as registers
 constexpr int TC = 4;   // consecutive p values per lane
+constexpr int US = BQ + 4;  // padded U row (words): 2-way instead of 16-way store conflicts for k-contiguous loads
 
 #ifndef AMSIM_CTAS1
 #define AMSIM_CTAS1 3
@@ -214,7 +215,7 @@ struct SmemLayout {
   static constexpr int BP = WP * 128;
   static constexpr int VS = BP + 4;  // padded row: conflict-free 4-row scatter
   static constexpr int V_WORDS = 2 * BK * VS;
-  static constexpr int U_WORDS = 2 * BK * BQ;
+  static constexpr int U_WORDS = 2 * BK * US;
   static constexpr int TILE_BYTES = (V_WORDS + U_WORDS) * 4;
   // tiles, then the table at the next multiple of its alignment
   static size_t bytes(int lut_bytes, int lut_align) { return (size_t)TILE_BYTES + lut_align + lut_bytes; }
@@ -267,6 +268,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 
   float4 vraw[2][2];  // [k group][row]
   float uraw[NU];
+  const bool u_kmajor = prm.u_sk == 1 && prm.u_sq != 1;
 
   auto load_tile = [&](int kb) {
 #pragma unroll
@@ -316,7 +318,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
-      const int kglob = kb * BK + (e >> 6), qg = q0 + (e & 63);
+      // lanes run along whichever index is contiguous in memory
+      const int kl = u_kmajor ? (e & (BK - 1)) : (e >> 6);
+      const int ql = u_kmajor ? (e >> 4) : (e & 63);
+      const int kglob = kb * BK + kl, qg = q0 + ql;
       float val = 0.f;
       if (kglob < prm.K && qg < prm.Q) {
         const uint32_t tap = fdiv((uint32_t)kglob, g.d_sc);
@@ -345,7 +350,9 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
-      Us[buf * BK * BQ + e] = enc_u(__float_as_uint(uraw[j]), prm.m);
+      const int kl = u_kmajor ? (e & (BK - 1)) : (e >> 6);
+      const int ql = u_kmajor ? (e >> 4) : (e & 63);
+      Us[buf * BK * US + kl * US + ql] = enc_u(__float_as_uint(uraw[j]), prm.m);
     }
   };
 
@@ -366,10 +373,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
     const int buf = kb & 1;
     if (kb + 1 < nkb) load_tile(kb + 1);
     const uint32_t* vs = Vs + buf * BK * VS + vcol;
-    const uint32_t* us = Us + buf * BK * BQ + ucol;
+    const uint32_t* us = Us + buf * BK * US + ucol;
 AMSIM_UNROLL_K
     for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT>(acc, vs + kk * VS, us + kk * BQ, lut_base, prm.rmask, prm.mult);
+      mac_step<EXACT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }
@@ -502,7 +509,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
-      Us[buf * BK * BQ + e] = enc_u(__float_as_uint(uraw[j]), prm.m);
+      Us[buf * BK * US + (e >> 6) * US + (e & 63)] = enc_u(__float_as_uint(uraw[j]), prm.m);
     }
   };
 
@@ -524,10 +531,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
     const int buf = kb & 1;
     if (kb + 1 < nkb) load_tile(kb + 1);
     const uint32_t* vs = Vs + buf * BK * VS + vcol;
-    const uint32_t* us = Us + buf * BK * BQ + ucol;
+    const uint32_t* us = Us + buf * BK * US + ucol;
 AMSIM_UNROLL_K
     for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT>(acc, vs + kk * VS, us + kk * BQ, lut_base, prm.rmask, prm.mult);
+      mac_step<EXACT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }
