@@ -1,0 +1,189 @@
+"""Layers over the AM ops, with the reference's gradient wiring.
+
+``AMConv2D`` and ``denseam`` mirror the Keras layers of the reference
+(python/keras/layers/am_convolutional.py:259-292, amdenselayer.py:180-227):
+the approximate op computes the linear part, bias add and activation are
+ordinary exact ops outside it.  Gradients are registered the way the reference
+does it in Python:
+
+* ``Convam``  -> ``ConvamInputGrad`` + ``ConvamFilterGrad``
+  (python/ops/amnn_ops.py:220-244),
+* ``Denseam`` -> ``DenseamGrad`` (amdenselayer.py:258-260),
+* ``MatMulAM`` -> ``dA = MatMulAM(g, B^T)``, ``dB = MatMulAM(A^T, g)`` with the
+  same LUT (the intent of python/ops/math_ops.py:127-157, whose code does not
+  forward the LUT).
+
+Activations are NHWC, filters HWIO, dense weights [in, out] — the reference's
+layouts, so weights are interchangeable with its Keras checkpoints.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from . import ops
+
+
+class _ConvamFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, strides, padding, lut, deterministic):
+        ctx.save_for_backward(x, w)
+        ctx.cfg = (strides, padding, lut, deterministic)
+        return ops.convam(x, w, strides=strides, padding=padding, mant_mul_lut=lut, deterministic=deterministic)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        strides, padding, lut, det = ctx.cfg
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = ops.convam_input_grad(x.shape, w, dy, strides=strides, padding=padding, mant_mul_lut=lut,
+                                       deterministic=det)
+        if ctx.needs_input_grad[1]:
+            dw = ops.convam_filter_grad(w.shape, x, dy, strides=strides, padding=padding, mant_mul_lut=lut,
+                                        deterministic=det)
+        return dx, dw, None, None, None, None
+
+
+class _DenseamFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, lut, deterministic):
+        ctx.save_for_backward(x, w)
+        ctx.cfg = (lut, deterministic)
+        return ops.denseam(x, w, lut, deterministic=deterministic)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        lut, det = ctx.cfg
+        dx, dw = ops.denseam_grad(g.contiguous(), x, w, lut, deterministic=det)
+        return dx, dw, None, None
+
+
+class _MatMulAMFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, lut, deterministic):
+        ctx.save_for_backward(a, b)
+        ctx.cfg = (lut, deterministic)
+        return ops.matmulam(a, b, mant_mul_lut=lut, deterministic=deterministic)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        lut, det = ctx.cfg
+        g = g.contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = ops.matmulam(g, b, transpose_b=True, mant_mul_lut=lut, deterministic=det)
+            if a.dim() == 2 and da.dim() == 3:
+                da = da.sum(0)
+        if ctx.needs_input_grad[1]:
+            db = ops.matmulam(a, g, transpose_a=True, mant_mul_lut=lut, deterministic=det)
+            if b.dim() == 2 and db.dim() == 3:
+                db = db.sum(0)
+        return da, db, None, None
+
+
+def amconv2d(x, w, strides=1, padding="VALID", mant_mul_lut="", deterministic=False):
+    return _ConvamFn.apply(x, w, strides, padding, mant_mul_lut, deterministic)
+
+
+def amdense(x, w, mant_mul_lut="", deterministic=False):
+    """AM dense on the last axis.  The reference's layer falls back to an exact
+    ``tensordot`` for rank > 2 inputs (amdenselayer.py:214-215); here the leading
+    axes are flattened so the approximate multiplier is used for every rank."""
+    lead = x.shape[:-1]
+    y = _DenseamFn.apply(x.reshape(-1, x.shape[-1]).contiguous(), w, mant_mul_lut, deterministic)
+    return y.reshape(*lead, w.shape[1])
+
+
+def ammatmul(a, b, mant_mul_lut="", deterministic=False):
+    """Batched AM matmul for rank >= 2 operands with equal leading axes (the op
+    itself takes rank 2/3: matmulam.cc:86-120; extra leading axes are folded
+    into the batch, which is what ammha/multihead_attention.py:18,30 needs)."""
+    if a.dim() > 3:
+        lead = a.shape[:-2]
+        out = _MatMulAMFn.apply(a.reshape(-1, *a.shape[-2:]).contiguous(), b.reshape(-1, *b.shape[-2:]).contiguous(),
+                                mant_mul_lut, deterministic)
+        return out.reshape(*lead, a.shape[-2], b.shape[-1])
+    return _MatMulAMFn.apply(a.contiguous(), b.contiguous(), mant_mul_lut, deterministic)
+
+
+_ACT = {None: lambda t: t, "linear": lambda t: t, "relu": torch.relu, "tanh": torch.tanh,
+        "softmax": lambda t: torch.softmax(t, -1)}
+
+
+class AMConv2D(nn.Module):
+    """2-D convolution with the approximate multiplier (am_convolutional.py AMConv2D).
+    NHWC in/out; kernel HWIO; ``padding`` 'valid' | 'same'."""
+
+    def __init__(self, in_channels, filters, kernel_size, strides=1, padding="valid", activation=None, use_bias=True,
+                 mant_mul_lut="", kernel_initializer="glorot_uniform", deterministic=False):
+        super().__init__()
+        kh, kw = (kernel_size, kernel_size) if isinstance(kernel_size, int) else kernel_size
+        self.strides = (strides, strides) if isinstance(strides, int) else tuple(strides)
+        self.padding = padding.upper()
+        self.activation = activation
+        self.mant_mul_lut = mant_mul_lut
+        self.deterministic = deterministic
+        self.kernel = nn.Parameter(torch.empty(kh, kw, in_channels, filters))
+        self.bias = nn.Parameter(torch.zeros(filters)) if use_bias else None
+        fan_in, fan_out = kh * kw * in_channels, kh * kw * filters
+        with torch.no_grad():
+            if kernel_initializer == "he_normal":
+                nn.init.trunc_normal_(self.kernel, std=math.sqrt(2.0 / fan_in) / 0.87962566103423978, a=-2 * math.sqrt(2.0 / fan_in) / 0.8796, b=2 * math.sqrt(2.0 / fan_in) / 0.8796)
+            else:
+                lim = math.sqrt(6.0 / (fan_in + fan_out))
+                self.kernel.uniform_(-lim, lim)
+
+    def forward(self, x):
+        y = amconv2d(x, self.kernel, [1, self.strides[0], self.strides[1], 1], self.padding, self.mant_mul_lut,
+                     self.deterministic)
+        if self.bias is not None:
+            y = y + self.bias
+        return _ACT[self.activation](y)
+
+
+class denseam(nn.Module):
+    """Dense layer with the approximate multiplier (amdenselayer.py denseam)."""
+
+    def __init__(self, in_features, units, activation=None, use_bias=True, mant_mul_lut="",
+                 kernel_initializer="glorot_uniform", deterministic=False):
+        super().__init__()
+        self.activation = activation
+        self.mant_mul_lut = mant_mul_lut
+        self.deterministic = deterministic
+        self.kernel = nn.Parameter(torch.empty(in_features, units))
+        self.bias = nn.Parameter(torch.zeros(units)) if use_bias else None
+        with torch.no_grad():
+            if kernel_initializer == "he_normal":
+                s = math.sqrt(2.0 / in_features)
+                nn.init.trunc_normal_(self.kernel, std=s / 0.8796, a=-2 * s / 0.8796, b=2 * s / 0.8796)
+            else:
+                lim = math.sqrt(6.0 / (in_features + units))
+                self.kernel.uniform_(-lim, lim)
+
+    def forward(self, x):
+        y = amdense(x, self.kernel, self.mant_mul_lut, self.deterministic)
+        if self.bias is not None:
+            y = y + self.bias
+        return _ACT[self.activation](y)
+
+
+# ---- exact helpers that keep activations physically NHWC --------------------------------------
+def nhwc_max_pool(x, k, s, padding=0):
+    return torch.nn.functional.max_pool2d(x.permute(0, 3, 1, 2), k, s, padding).permute(0, 2, 3, 1)
+
+
+def nhwc_avg_pool(x, k, s):
+    return torch.nn.functional.avg_pool2d(x.permute(0, 3, 1, 2), k, s).permute(0, 2, 3, 1)
+
+
+class BatchNormNHWC(nn.BatchNorm2d):
+    """Exact batch normalisation on an NHWC tensor (viewed as channels-last NCHW)."""
+
+    def forward(self, x):
+        return super().forward(x.permute(0, 3, 1, 2)).permute(0, 2, 3, 1)
