@@ -15,6 +15,9 @@
 #include <string>
 #include <vector>
 
+#ifndef AMSIM_CTAS1
+#define AMSIM_CTAS1 3
+#endif
 #include "amsim_kernels.cuh"
 
 using namespace amsim;
@@ -173,14 +176,47 @@ void fill_gather_divs(Gather& g) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <int WP, bool EXACT, bool VEC>
-int launch_gather_t(cudaStream_t st, const Params& p, int batch, int device) {
+int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   using L = SmemLayout<WP>;
-  const size_t smem = L::bytes(p.lut_bytes, p.lut_align);
-  int rc = ensure_smem(gather_gemm<WP, EXACT, VEC>, smem, device);
+  const int ptiles = (p.P + L::BP - 1) / L::BP, qtiles = (p.Q + BQ - 1) / BQ;
+  // Fast mode: when the tiles alone cannot fill the resident CTA slots, a
+  // thread-block cluster of `ksplit` CTAs shares each tile's reduction.
+  int ksplit = 1;
+  if (!EXACT && WP == 1) {
+    const long long ctas = (long long)ptiles * qtiles * batch;
+    const int slots = 148 * AMSIM_CTAS1;
+    const int nkb = (p.K + BK - 1) / BK;
+    while (ksplit < 8 && ctas * (ksplit * 2) <= slots && nkb / (ksplit * 2) >= 6) ksplit *= 2;
+    if (const char* f = getenv("AMSIM_FORCE_KSPLIT")) ksplit = atoi(f) > 0 ? atoi(f) : 1;
+  }
+  p.ksplit = ksplit;
+  p.tile_bytes = L::TILE_BYTES;
+  if (ksplit > 1 && L::EXCHANGE_BYTES > p.tile_bytes) p.tile_bytes = L::EXCHANGE_BYTES;
+  const size_t smem = L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
+  if (ksplit == 1) {
+    int rc = ensure_smem(gather_gemm<WP, EXACT, VEC, false>, smem, device);
+    if (rc) return rc;
+    gather_gemm<WP, EXACT, VEC, false><<<dim3(ptiles, qtiles, batch), L::NT, smem, st>>>(p);
+    CUDA_TRY(cudaGetLastError());
+    return AMSIM_OK;
+  }
+  constexpr bool kCanCluster = !EXACT && WP == 1;
+  int rc = ensure_smem(gather_gemm<WP, EXACT, VEC, kCanCluster>, smem, device);
   if (rc) return rc;
-  dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, batch);
-  gather_gemm<WP, EXACT, VEC><<<grid, L::NT, smem, st>>>(p);
-  CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(ptiles * ksplit, qtiles, batch);
+  cfg.blockDim = dim3(L::NT, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = ksplit;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, gather_gemm<WP, EXACT, VEC, kCanCluster>, p));
   return AMSIM_OK;
 }
 
@@ -188,11 +224,9 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
   if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
   if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
-  // Tile height: the one that leaves the busiest SM with fewer rows to process.
-  const long long qb = (long long)((p.Q + BQ - 1) / BQ) * batch;
-  const long long rows1 = (((long long)((p.P + 127) / 128) * qb + 147) / 148) * 128;
-  const long long rows2 = (((long long)((p.P + 255) / 256) * qb + 147) / 148) * 256;
-  bool wide = rows2 < rows1;
+  // 128-row tiles (3 CTAs of 4 warps per SM, no register cap) measured faster than
+  // 256-row tiles on every shape tried; the taller tile stays selectable for experiments.
+  bool wide = false;
   if (const char* f = getenv("AMSIM_FORCE_WP")) wide = atoi(f) == 2;
 #define AMSIM_GO(WP_, EX_, VEC_) return launch_gather_t<WP_, EX_, VEC_>(st, p, batch, device)
   if (wide) {
@@ -237,7 +271,7 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
 template <int WP, bool EXACT, bool VEC>
 int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   using L = SmemLayout<WP>;
-  const size_t smem = L::bytes(p.lut_bytes, p.lut_align);
+  const size_t smem = L::bytes(L::TILE_BYTES, p.lut_bytes, p.lut_align);
   int rc = ensure_smem(fgrad_gemm<WP, EXACT, VEC>, smem, device);
   if (rc) return rc;
   dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, p.splits);

@@ -30,6 +30,7 @@
 // uniform operand is packed into ONE word per element.  Tensor cores cannot be
 // used: no product is a hardware multiply.
 #pragma once
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -116,6 +117,10 @@ struct Params {
   uint32_t rowstride;           // 1 << m
   uint32_t rmask;               // ((1 << m) - 1) << m : row bits of a table address
   uint32_t lut_align;           // power of two >= lut_bytes: alignment of the table in shared memory
+  // gather_gemm, fast mode: CTAs of one thread-block cluster split the reduction and
+  // combine their register tiles through distributed shared memory (1 = no split)
+  int ksplit;
+  int tile_bytes;               // bytes reserved before the table (operand tiles, or the exchange buffer)
   // fgrad only
   int k_chunk, splits;
   float* ws;                    // [splits][P][Q] partial sums when splits > 1
@@ -218,13 +223,14 @@ struct SmemLayout {
   static constexpr int U_WORDS = 2 * BK * US;
   static constexpr int TILE_BYTES = (V_WORDS + U_WORDS) * 4;
   // tiles, then the table at the next multiple of its alignment
-  static size_t bytes(int lut_bytes, int lut_align) { return (size_t)TILE_BYTES + lut_align + lut_bytes; }
+  static constexpr int EXCHANGE_BYTES = TR * TC * NT * 4;  // one register tile per thread
+  static size_t bytes(int tile_bytes, int lut_bytes, int lut_align) { return (size_t)tile_bytes + lut_align + lut_bytes; }
 };
 
 // -----------------------------------------------------------------------------
 // gather_gemm: V gathered along k.  grid = (ceil(P/BP), ceil(Q/64), batch).
 // -----------------------------------------------------------------------------
-template <int WP, bool EXACT, bool VEC>
+template <int WP, bool EXACT, bool VEC, bool CLUSTER>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
@@ -234,12 +240,14 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);
   uint32_t* Us = Vs + L::V_WORDS;
   const uint32_t smem_base = smem_addr(smem);
-  const uint32_t lut_base = (smem_base + L::TILE_BYTES + prm.lut_align - 1) & ~(prm.lut_align - 1);
+  const uint32_t lut_base = (smem_base + prm.tile_bytes + prm.lut_align - 1) & ~(prm.lut_align - 1);
   uint8_t* lut_s = smem + (lut_base - smem_base);
 
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
   const int wp = w % WP, wq = w / WP;
-  const int p0 = blockIdx.x * BP, q0 = blockIdx.y * BQ;
+  const int ksplit = CLUSTER ? prm.ksplit : 1;   // cluster size along x
+  const int krank = blockIdx.x % ksplit;         // this CTA's slice of the reduction
+  const int p0 = (blockIdx.x / ksplit) * BP, q0 = blockIdx.y * BQ;
   const float* __restrict__ Vg = prm.V + (long long)blockIdx.z * prm.v_bs;
   const float* __restrict__ Ug = prm.U + (long long)blockIdx.z * prm.u_bs;
   float* __restrict__ Og = prm.O + (long long)blockIdx.z * prm.o_bs;
@@ -362,15 +370,20 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 #pragma unroll
     for (int c = 0; c < TC; ++c) acc[r][c] = 0.f;
 
-  const int nkb = (prm.K + BK - 1) / BK;
-  load_tile(0);
-  store_tile(0);
+  const int nkb_all = (prm.K + BK - 1) / BK;
+  const int per = (nkb_all + ksplit - 1) / ksplit;
+  const int kb_begin = krank * per;
+  const int nkb = min(kb_begin + per, nkb_all);
+  if (kb_begin < nkb) {
+    load_tile(kb_begin);
+    store_tile(0);
+  }
   __syncthreads();
 
   const int vcol = wp * 128 + 4 * lane;
   const int ucol = wq * TR;
-  for (int kb = 0; kb < nkb; ++kb) {
-    const int buf = kb & 1;
+  for (int kb = kb_begin; kb < nkb; ++kb) {
+    const int buf = (kb - kb_begin) & 1;
     if (kb + 1 < nkb) load_tile(kb + 1);
     const uint32_t* vs = Vs + buf * BK * VS + vcol;
     const uint32_t* us = Us + buf * BK * US + ucol;
@@ -379,6 +392,32 @@ AMSIM_UNROLL_K
       mac_step<EXACT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
+  }
+
+  // ---- cluster reduction: ranks 1.. park their register tiles in their own shared
+  // memory, rank 0 adds them in rank order through distributed shared memory ----------
+  if (CLUSTER) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    float* red = reinterpret_cast<float*>(smem);  // [TR*TC][NT], the operand tiles are dead now
+    if (krank != 0) {
+#pragma unroll
+      for (int r = 0; r < TR; ++r)
+#pragma unroll
+        for (int c = 0; c < TC; ++c) red[(r * TC + c) * NT + t] = acc[r][c];
+    }
+    cluster.sync();
+    if (krank == 0) {
+      for (int src = 1; src < ksplit; ++src) {
+        const float* remote = cluster.map_shared_rank(red, src);
+#pragma unroll
+        for (int r = 0; r < TR; ++r)
+#pragma unroll
+          for (int c = 0; c < TC; ++c) acc[r][c] = __fadd_rn(acc[r][c], remote[(r * TC + c) * NT + t]);
+      }
+    }
+    cluster.sync();  // keep the senders' shared memory alive until it has been read
+    if (krank != 0) return;
   }
 
   // ---- epilogue ---------------------------------------------------------------

@@ -120,6 +120,7 @@ def run_conv3_gpu(args, rank, world):
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    args.lut = args.lut or "MBM_7"
     lut = os.path.join(LUT_DIR, args.lut + ".bin")
     peaks = measured_peaks()
     work = conv3_work()
@@ -277,6 +278,213 @@ def run_conv3_gpu(args, rank, world):
 
 
 # ------------------------------------------------------------------------------------------------
+TRAIN_WORKLOADS = {
+    # name: (metric, unit, per-GPU batch, LUT, description)
+    "resnet50": ("resnet50_am_train_throughput", "img/s", 32, "MBM_7",
+                 "ResNet-50 v1 bottleneck, every Conv2D -> AMConv2D and the FC -> denseam, 224x224x3 NHWC ~N(0,1), "
+                 "uniform labels 0..999, He-normal init, SGD train step"),
+    "transformer": ("transformer_am_train_throughput", "tokens/s", 64, "MIT_7",
+                    "Transformer encoder-decoder 6+6 layers, d_model 512, 8 heads, FFN 2048, seq 128, vocab 8000, "
+                    "AMMHA + MatMulAM + denseam, teacher-forced SGD train step"),
+    "lenet5": ("lenet5_am_train_throughput", "img/s", 128, "MIT_7", "LeNet-5 AMConv2D + denseam, 28x28x1, SGD train step"),
+    "lenet300100": ("lenet300100_am_train_throughput", "img/s", 256, "MBM_7", "LeNet-300-100 denseam, 784 inputs, SGD train step"),
+}
+
+
+class OpTimer:
+    """Wraps the op functions so every call is bracketed by CUDA events on the
+    current stream and attributed its product count."""
+
+    def __init__(self, ops_mod, torch):
+        self.ops, self.torch = ops_mod, torch
+        self.records = []  # (kernel, macs, e0, e1)
+        self.enabled = False
+        self.launches = 0
+        self._orig = {}
+
+    def _wrap(self, name, kernel, macs_fn, launches_fn=lambda *a, **k: 1):
+        orig = getattr(self.ops, name)
+        self._orig[name] = orig
+
+        def f(*a, **k):
+            if not self.enabled:
+                return orig(*a, **k)
+            e0 = self.torch.cuda.Event(enable_timing=True)
+            e1 = self.torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = orig(*a, **k)
+            e1.record()
+            self.records.append((kernel, macs_fn(out, *a, **k), e0, e1))
+            self.launches += launches_fn(out, *a, **k)
+            return out
+        setattr(self.ops, name, f)
+
+    def install(self):
+        def conv_macs(out, x, w, **k):
+            return out.numel() * w.shape[0] * w.shape[1] * w.shape[2]
+
+        def igrad_macs(out, sizes, w, dy, **k):
+            return dy.numel() * w.shape[0] * w.shape[1] * w.shape[2]
+
+        def fgrad_macs(out, sizes, x, dy, **k):
+            return dy.numel() * sizes[0] * sizes[1] * sizes[2]
+
+        self._wrap("convam", "gather_gemm", conv_macs)
+        self._wrap("convam_input_grad", "gather_gemm", igrad_macs)
+        self._wrap("convam_filter_grad", "fgrad_gemm", fgrad_macs, lambda *a, **k: 2)
+        self._wrap("denseam", "gather_gemm", lambda out, x, w, *a, **k: out.numel() * x.shape[1])
+        self._wrap("denseam_grad", "dense_grad(gather+fgrad)", lambda out, g, x, w, *a, **k: 2 * x.numel() * w.shape[1],
+                   lambda *a, **k: 3)
+        self._wrap("matmulam", "gather_gemm", lambda out, a, b, **k: out.numel() * a.shape[-1 if not k.get("transpose_a") else -2])
+
+    def summary(self, steps):
+        agg = {}
+        for kernel, macs, e0, e1 in self.records:
+            a = agg.setdefault(kernel, [0, 0.0, 0])
+            a[0] += macs
+            a[1] += e0.elapsed_time(e1)
+            a[2] += 1
+        return {k: {"macs_per_step": v[0] // steps, "ms_per_step": v[1] / steps, "calls_per_step": v[2] // steps} for k, v in agg.items()}
+
+
+def build_train_workload(name, lut, dev, rank, torch, deterministic):
+    from approxtrain_b200 import nets
+    metric, unit, batch, _, _ = TRAIN_WORKLOADS[name]
+    torch.manual_seed(0)  # identical weights on every rank
+    g = torch.Generator().manual_seed(1000 + rank)  # different data shard per rank
+    if name == "resnet50":
+        model = nets.ResNet50AM(lut, deterministic=deterministic).to(dev)
+        hx = torch.randn(batch, 224, 224, 3, generator=g).pin_memory()
+        hy = torch.randint(0, 1000, (batch,), generator=g).pin_memory()
+        units = batch
+
+        def loss_fn(x, y):
+            return torch.nn.functional.cross_entropy(model(x), y)
+    elif name == "transformer":
+        model = nets.TransformerAM(lut, deterministic=deterministic).to(dev)
+        hx = torch.randint(1, 8000, (batch, 128), generator=g).pin_memory()
+        hy = torch.randint(1, 8000, (batch, 129), generator=g).pin_memory()
+        units = batch * 128
+
+        def loss_fn(x, y):
+            logits = model(x, y[:, :-1])
+            return torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]), y[:, 1:].reshape(-1))
+    elif name == "lenet5":
+        model = nets.LeNet5(lut, deterministic=deterministic).to(dev)
+        hx = torch.rand(batch, 28, 28, 1, generator=g).pin_memory()
+        hy = torch.randint(0, 10, (batch,), generator=g).pin_memory()
+        units = batch
+
+        def loss_fn(x, y):
+            return torch.nn.functional.cross_entropy(model(x), y)
+    else:
+        model = nets.LeNet300100(lut, deterministic=deterministic).to(dev)
+        hx = torch.rand(batch, 28, 28, 1, generator=g).pin_memory()
+        hy = torch.randint(0, 10, (batch,), generator=g).pin_memory()
+        units = batch
+
+        def loss_fn(x, y):
+            return torch.nn.functional.cross_entropy(model(x), y)
+    return model, hx, hy, units, loss_fn
+
+
+def run_train_gpu(args, rank, world):
+    import torch
+    import torch.distributed as dist
+    from approxtrain_b200 import ops
+    from approxtrain_b200.dp import DataParallelSGD
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    metric, unit, batch, default_lut, desc = TRAIN_WORKLOADS[args.workload]
+    lut_name = args.lut or default_lut
+    lut = os.path.join(LUT_DIR, lut_name + ".bin")
+    peaks = measured_peaks()
+    timer = OpTimer(ops, torch)
+    timer.install()
+    model, hx, hy, units, loss_fn = build_train_workload(args.workload, lut, dev, rank, torch, args.deterministic)
+    trainer = DataParallelSGD(model, lr=1e-3)
+    dx, dy = hx.to(dev), hy.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        trainer.step(lambda: loss_fn(dx, dy))
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    timer.enabled = True
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        loss = trainer.step(lambda: loss_fn(dx, dy))
+    t1.record()
+    barrier()
+    timer.enabled = False
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t0.elapsed_time(t1)
+    if world > 1:
+        tt = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        total_ms = float(tt.item())
+    value = world * units * args.steps / (total_ms * 1e-3)
+
+    # ---- end to end: this step's batch starts in pinned host memory, the loss comes back to the host
+    e2e_steps = max(1, min(args.steps, 5))
+    barrier()
+    w0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        x = hx.to(dev, non_blocking=True)
+        y = hy.to(dev, non_blocking=True)
+        host_loss = float(trainer.step(lambda: loss_fn(x, y)).item())
+    barrier()
+    e2e_s = time.perf_counter() - w0
+    if world > 1:
+        tt = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_s = float(tt.item())
+    if rank != 0:
+        return None
+    issue_peak = LANES_PER_CLK_PER_SM * N_SM * peaks["sm_max_mhz"] * 1e6 / 1e12
+    summ = timer.summary(args.steps)
+    am_ms = sum(v["ms_per_step"] for v in summ.values())
+    am_macs = sum(v["macs_per_step"] for v in summ.values())
+    dom = max(summ, key=lambda k: summ[k]["ms_per_step"]) if summ else None
+    roofline = None
+    if dom:
+        ach = summ[dom]["macs_per_step"] / (summ[dom]["ms_per_step"] * 1e-3) / 1e12
+        roofline = {"kernel": dom, "bound": "lut-issue", "achieved": round(ach, 4), "peak": round(issue_peak, 4),
+                    "unit": "TMAC/s", "frac": round(ach / issue_peak, 4),
+                    "peak_def": f"32 lookups/clk/SM x {N_SM} SM x sm_max_mhz {peaks['sm_max_mhz']:.0f} ({peaks['source']})",
+                    "launches_per_step": summ[dom]["calls_per_step"], "traffic": None,
+                    "note": "aggregate over all launches of this kernel in a step (many layer shapes); per-shape figures: --workload conv3"}
+    return {
+        "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(total_ms / args.steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {desc}", "per_gpu_batch": batch, "global_batch": batch * world,
+                   "lut": lut_name, "mode": "deterministic" if args.deterministic else "fast",
+                   "parallelism": f"dp{world}: batch sharded, NCCL all-reduce of {trainer.gradient_bytes() / 1e6:.1f} MB of gradients per step",
+                   "l2": "inputs larger than L2: a step streams activations and gradients far beyond 126 MB" if args.workload in ("resnet50", "transformer") else "working set smaller than L2 (launch-bound network)"},
+        "clocks": clocks,
+        "e2e": {"value": round(world * units * e2e_steps / e2e_s, 2), "unit": unit,
+                "h2d_bytes_per_step": hx.numel() * hx.element_size() + hy.numel() * hy.element_size(),
+                "d2h_bytes_per_step": 4, "steps": e2e_steps, "loss": host_loss},
+        "gpu_launches": timer.launches,
+        "roofline": roofline,
+        "am_ops": {"ms_per_step": round(am_ms, 3), "gmac_per_step": round(am_macs / 1e9, 2),
+                   "share_of_step": round(am_ms / (total_ms / args.steps), 3), "by_kernel": {k: {kk: (round(vv, 3) if isinstance(vv, float) else vv) for kk, vv in v.items()} for k, v in summ.items()}},
+    }
+
+
+# ------------------------------------------------------------------------------------------------
 def cpu_conv3(sample_batch: int, repeats: int = 1):
     """The reference's CPU op path (exact multiply, serial loops: convam.cc:452-491,
     :639-686, :910-954) restated in oracle/amsim_oracle.c, on a batch-reduced
@@ -337,8 +545,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="conv3", choices=["conv3"])
-    ap.add_argument("--lut", default="MBM_7")
+    ap.add_argument("--workload", default="conv3", choices=["conv3"] + list(TRAIN_WORKLOADS))
+    ap.add_argument("--lut", default=None)
     ap.add_argument("--deterministic", action="store_true")
     ap.add_argument("--cpu-sample-batch", type=int, default=4)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -360,9 +568,11 @@ def main():
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
         dist.init_process_group("nccl")
     try:
-        line = run_conv3_gpu(args, rank, world)
+        line = run_conv3_gpu(args, rank, world) if args.workload == "conv3" else run_train_gpu(args, rank, world)
         if rank == 0:
-            if world == 1 and not args.no_cpu_baseline:
+            if args.workload != "conv3":
+                line["cpu_baseline"] = None
+            elif world == 1 and not args.no_cpu_baseline:
                 v, s, desc = cpu_conv3(args.cpu_sample_batch)
                 line["cpu_baseline"] = {"value": round(v, 3), "unit": "GMAC/s", "cores": 1, "host_cores": os.cpu_count(),
                                         "kind": "port", "sample": desc, "seconds": round(s, 2)}

@@ -359,3 +359,26 @@ def test_full_size_properties_config3_shapeB(ops):
     # exact-multiply sanity: the AM result tracks the exact convolution within the multiplier's error
     ref = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2), w.permute(3, 2, 0, 1), padding=1).permute(0, 2, 3, 1)
     assert rel_l2(y.cpu().numpy(), ref.cpu().numpy()) < 0.1
+
+
+@pytest.mark.parametrize("force", [None, "2", "4", "8"])
+def test_cluster_split_of_the_reduction(ops, oracle, luts, force, monkeypatch):
+    """Few output tiles and a long reduction: the fast path lets a thread-block
+    cluster share each tile's reduction and adds the partial tiles in rank order
+    through distributed shared memory.  Deterministic mode never splits."""
+    lut, m = luts["MBM_7"]
+    rng = np.random.default_rng(31)
+    x, wt = _conv_case(rng, 2, 7, 7, 64, 3, 3, 96)          # 98 pixels, 2 channel tiles, K = 576 (36 stages)
+    g = oracle.geometry(2, 7, 7, 64, 3, 3, 96, 1, 1, "SAME")
+    dy = rng.standard_normal((2, 7, 7, 96)).astype(np.float32)
+    if force is not None:
+        monkeypatch.setenv("AMSIM_FORCE_KSPLIT", force)
+    kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=lut_path("MBM_7"))
+    y = ops.convam(dev(x), dev(wt), **kw_).cpu().numpy()
+    dx = ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_).cpu().numpy()
+    y2 = ops.convam(dev(x), dev(wt), **kw_).cpu().numpy()
+    assert_close(y, oracle.conv2d_fwd(g, x, wt, lut, m), f"cluster split fwd ({force})")
+    assert_close(dx, oracle.conv2d_bwd_input(g, wt, dy, lut, m), f"cluster split input-grad ({force})")
+    assert np.array_equal(y, y2), "rank-ordered combine: run-to-run identical"
+    yd = ops.convam(dev(x), dev(wt), deterministic=True, **kw_).cpu().numpy()
+    assert_bit_equal(yd, oracle.conv2d_fwd(g, x, wt, lut, m), "deterministic mode ignores the split")
