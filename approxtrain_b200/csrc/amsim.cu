@@ -48,7 +48,8 @@ struct amsim_lut {
   int device = 0;
   int refs = 0;
   std::string key;
-  uint8_t* d_raw = nullptr;    // 2^(2m) bytes as in the file
+  uint8_t* d_raw = nullptr;    // 2^(2m) bytes as in the file (row = first operand)
+  uint8_t* d_raw_t = nullptr;  // the same bytes transposed (row = second operand)  [m > 7]
   uint8_t* d_canon = nullptr;  // encoded, row = first operand (a)   [m <= 7]
   uint8_t* d_trans = nullptr;  // encoded, row = second operand (b)  [m <= 7]
   int enc_bytes = 0;           // size of each encoded copy, multiple of 16
@@ -113,8 +114,18 @@ int upload_lut(const uint8_t* bytes, int m, int device, amsim_lut** out) {
     if (e == cudaSuccess) e = cudaMemcpy(h->d_trans, trans.data(), h->enc_bytes, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) bail(e, "upload of encoded lut");
   }
+  if (rc == AMSIM_OK && m > 7) {
+    const size_t side = (size_t)1 << m;
+    std::vector<uint8_t> tr(n);
+    for (size_t a = 0; a < side; ++a)
+      for (size_t b = 0; b < side; ++b) tr[b * side + a] = bytes[a * side + b];
+    e = cudaMalloc(&h->d_raw_t, n);
+    if (e == cudaSuccess) e = cudaMemcpy(h->d_raw_t, tr.data(), n, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) bail(e, "upload of transposed lut");
+  }
   cudaSetDevice(prev);
   if (rc != AMSIM_OK) {
+    cudaFree(h->d_raw_t);
     cudaFree(h->d_raw);
     cudaFree(h->d_canon);
     cudaFree(h->d_trans);
@@ -128,8 +139,7 @@ int upload_lut(const uint8_t* bytes, int m, int device, amsim_lut** out) {
 int check_common(const amsim_lut* lut, unsigned flags, bool need_gemm) {
   if (!lut) return fail(AMSIM_ERR_INVALID, "lut handle is NULL");
   if (flags & ~AMSIM_DETERMINISTIC) return fail(AMSIM_ERR_INVALID, "unknown flag bits 0x%x", flags);
-  if (need_gemm && lut->m > 7)
-    return fail(AMSIM_ERR_UNSUPPORTED, "GEMM kernels hold the table in shared memory: m = %d > 7 is not supported", lut->m);
+  (void)need_gemm;
   int dev = -1;
   CUDA_TRY(cudaGetDevice(&dev));
   if (dev != lut->device)
@@ -159,9 +169,12 @@ void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
   p.mult = 1u << (23 - lut->m);
   p.rowstride = 1u << lut->m;
   p.rmask = ((1u << lut->m) - 1u) << lut->m;
+  p.cmask = (1u << lut->m) - 1u;
+  p.cadj = (1u << 23) - 128u * p.mult;
+  p.lut_raw = v_is_first_operand ? lut->d_raw_t : lut->d_raw;
   uint32_t al = 16;
   while (al < (uint32_t)lut->enc_bytes) al <<= 1;
-  p.lut_align = al;
+  p.lut_align = al;  // m > 7: no table in shared memory (enc_bytes = 0)
 }
 
 void fill_gather_divs(Gather& g) {
@@ -175,14 +188,14 @@ void fill_gather_divs(Gather& g) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-template <int WP, bool EXACT, bool VEC>
+template <bool EXACT, bool VEC, bool GLUT>
 int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
-  using L = SmemLayout<WP>;
+  using L = SmemLayout<1>;
   const int ptiles = (p.P + L::BP - 1) / L::BP, qtiles = (p.Q + BQ - 1) / BQ;
   // Fast mode: when the tiles alone cannot fill the resident CTA slots, a
   // thread-block cluster of `ksplit` CTAs shares each tile's reduction.
   int ksplit = 1;
-  if (!EXACT && WP == 1) {
+  if (!EXACT && !GLUT) {
     const long long ctas = (long long)ptiles * qtiles * batch;
     const int slots = 148 * AMSIM_CTAS1;
     const int nkb = (p.K + BK - 1) / BK;
@@ -192,16 +205,16 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   p.ksplit = ksplit;
   p.tile_bytes = L::TILE_BYTES;
   if (ksplit > 1 && L::EXCHANGE_BYTES > p.tile_bytes) p.tile_bytes = L::EXCHANGE_BYTES;
-  const size_t smem = L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
+  const size_t smem = GLUT ? (size_t)p.tile_bytes + 16 : L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
   if (ksplit == 1) {
-    int rc = ensure_smem(gather_gemm<WP, EXACT, VEC, false>, smem, device);
+    int rc = ensure_smem(gather_gemm<1, EXACT, VEC, false, GLUT>, smem, device);
     if (rc) return rc;
-    gather_gemm<WP, EXACT, VEC, false><<<dim3(ptiles, qtiles, batch), L::NT, smem, st>>>(p);
+    gather_gemm<1, EXACT, VEC, false, GLUT><<<dim3(ptiles, qtiles, batch), L::NT, smem, st>>>(p);
     CUDA_TRY(cudaGetLastError());
     return AMSIM_OK;
   }
-  constexpr bool kCanCluster = !EXACT && WP == 1;
-  int rc = ensure_smem(gather_gemm<WP, EXACT, VEC, kCanCluster>, smem, device);
+  constexpr bool kCanCluster = !EXACT && !GLUT;
+  int rc = ensure_smem(gather_gemm<1, EXACT, VEC, kCanCluster, GLUT>, smem, device);
   if (rc) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -216,7 +229,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, gather_gemm<WP, EXACT, VEC, kCanCluster>, p));
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, gather_gemm<1, EXACT, VEC, kCanCluster, GLUT>, p));
   return AMSIM_OK;
 }
 
@@ -224,17 +237,14 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
   if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
   if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
-  // 128-row tiles (3 CTAs of 4 warps per SM, no register cap) measured faster than
-  // 256-row tiles on every shape tried; the taller tile stays selectable for experiments.
-  bool wide = false;
-  if (const char* f = getenv("AMSIM_FORCE_WP")) wide = atoi(f) == 2;
-#define AMSIM_GO(WP_, EX_, VEC_) return launch_gather_t<WP_, EX_, VEC_>(st, p, batch, device)
-  if (wide) {
-    if (exact) { if (vec) AMSIM_GO(2, true, true); else AMSIM_GO(2, true, false); }
-    else       { if (vec) AMSIM_GO(2, false, true); else AMSIM_GO(2, false, false); }
+  const bool glut = p.m > 7;  // table too large for shared memory: global / L2 lookups
+#define AMSIM_GO(EX_, VEC_, GL_) return launch_gather_t<EX_, VEC_, GL_>(st, p, batch, device)
+  if (glut) {
+    if (exact) { if (vec) AMSIM_GO(true, true, true); else AMSIM_GO(true, false, true); }
+    else       { if (vec) AMSIM_GO(false, true, true); else AMSIM_GO(false, false, true); }
   } else {
-    if (exact) { if (vec) AMSIM_GO(1, true, true); else AMSIM_GO(1, true, false); }
-    else       { if (vec) AMSIM_GO(1, false, true); else AMSIM_GO(1, false, false); }
+    if (exact) { if (vec) AMSIM_GO(true, true, false); else AMSIM_GO(true, false, false); }
+    else       { if (vec) AMSIM_GO(false, true, false); else AMSIM_GO(false, false, false); }
   }
 #undef AMSIM_GO
 }
@@ -247,7 +257,6 @@ struct FgradPlan {
 FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
   FgradPlan f;
   f.wp = 1;  // 128-row tiles: 3 CTAs of 4 warps per SM without register spills
-  if (const char* e = getenv("AMSIM_FORCE_WP")) f.wp = atoi(e) == 2 ? 2 : 1;
   const int bp = f.wp * 128;
   const int slots = 148 * (f.wp == 1 ? 3 : 2);  // resident CTAs on the whole GPU
   const long long tiles = (long long)((P + bp - 1) / bp) * ((Q + BQ - 1) / BQ);
@@ -268,14 +277,14 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
   return f;
 }
 
-template <int WP, bool EXACT, bool VEC>
+template <bool EXACT, bool VEC, bool GLUT>
 int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
-  using L = SmemLayout<WP>;
-  const size_t smem = L::bytes(L::TILE_BYTES, p.lut_bytes, p.lut_align);
-  int rc = ensure_smem(fgrad_gemm<WP, EXACT, VEC>, smem, device);
+  using L = SmemLayout<1>;
+  const size_t smem = GLUT ? (size_t)L::TILE_BYTES + 16 : L::bytes(L::TILE_BYTES, p.lut_bytes, p.lut_align);
+  int rc = ensure_smem(fgrad_gemm<1, EXACT, VEC, GLUT>, smem, device);
   if (rc) return rc;
   dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, p.splits);
-  fgrad_gemm<WP, EXACT, VEC><<<grid, L::NT, smem, st>>>(p);
+  fgrad_gemm<1, EXACT, VEC, GLUT><<<grid, L::NT, smem, st>>>(p);
   CUDA_TRY(cudaGetLastError());
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
@@ -297,13 +306,14 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   p.k_chunk = f.k_chunk;
   p.ws = static_cast<float*>(ws);
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
-#define AMSIM_GO(WP_, EX_, VEC_) return launch_fgrad_t<WP_, EX_, VEC_>(st, p, device)
-  if (f.wp == 2) {
-    if (exact) { if (vec) AMSIM_GO(2, true, true); else AMSIM_GO(2, true, false); }
-    else       { if (vec) AMSIM_GO(2, false, true); else AMSIM_GO(2, false, false); }
+  const bool glut = p.m > 7;
+#define AMSIM_GO(EX_, VEC_, GL_) return launch_fgrad_t<EX_, VEC_, GL_>(st, p, device)
+  if (glut) {
+    if (exact) { if (vec) AMSIM_GO(true, true, true); else AMSIM_GO(true, false, true); }
+    else       { if (vec) AMSIM_GO(false, true, true); else AMSIM_GO(false, false, true); }
   } else {
-    if (exact) { if (vec) AMSIM_GO(1, true, true); else AMSIM_GO(1, true, false); }
-    else       { if (vec) AMSIM_GO(1, false, true); else AMSIM_GO(1, false, false); }
+    if (exact) { if (vec) AMSIM_GO(true, true, false); else AMSIM_GO(true, false, false); }
+    else       { if (vec) AMSIM_GO(false, true, false); else AMSIM_GO(false, false, false); }
   }
 #undef AMSIM_GO
 }
@@ -378,6 +388,7 @@ int amsim_lut_close(amsim_lut* lut) {
   cudaGetDevice(&prev);
   cudaSetDevice(lut->device);
   cudaFree(lut->d_raw);
+  cudaFree(lut->d_raw_t);
   cudaFree(lut->d_canon);
   cudaFree(lut->d_trans);
   cudaSetDevice(prev);

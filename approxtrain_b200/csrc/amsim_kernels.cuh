@@ -116,6 +116,9 @@ struct Params {
   uint32_t mult;                // 1 << (23 - m)
   uint32_t rowstride;           // 1 << m
   uint32_t rmask;               // ((1 << m) - 1) << m : row bits of a table address
+  uint32_t cmask;               // (1 << m) - 1        : column bits
+  uint32_t cadj;                // global-table path: 2^23 - 128 * mult (carry bit of a raw byte)
+  const uint8_t* lut_raw;       // global-table path (m > 7): raw bytes, rows by the uniform operand
   uint32_t lut_align;           // power of two >= lut_bytes: alignment of the table in shared memory
   // gather_gemm, fast mode: CTAs of one thread-block cluster split the reduction and
   // combine their register tiles through distributed shared memory (1 = no split)
@@ -154,10 +157,13 @@ __device__ __forceinline__ uint32_t enc_v(uint32_t bits, int m) {
 //   vrow : 4 consecutive lane-operand words (sign+exponent | column)
 //   urow : 16 uniform-operand words (sign+exponent | column << m)
 //   lut_base : shared-memory address of the table (aligned to its size)
-template <bool EXACT>
+//   GLUT : the table stays in global memory (L2-resident, m = 8..11) as raw bytes;
+//          lut_base is then unused and `lut_g` points at the table.
+template <bool EXACT, bool GLUT>
 __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* __restrict__ vrow,
                                          const uint32_t* __restrict__ urow, const uint32_t lut_base,
-                                         const uint32_t rmask, const uint32_t mult) {
+                                         const uint32_t rmask, const uint32_t mult, const uint32_t cmask,
+                                         const uint32_t cadj, const uint8_t* __restrict__ lut_g) {
   const uint4 cw = *reinterpret_cast<const uint4*>(vrow);
   const uint32_t w[TC] = {cw.x, cw.y, cw.z, cw.w};
   uint32_t ci[TC], cs[TC];
@@ -165,7 +171,7 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
   bool nz[TC];
 #pragma unroll
   for (int t = 0; t < TC; ++t) {
-    ci[t] = (w[t] & 0xFFu) | lut_base;
+    ci[t] = GLUT ? (w[t] & cmask) : ((w[t] & 0xFFu) | lut_base);
     nz[t] = w[t] != 0u;
     if (EXACT) {
       // AMsimulator.inl:26-33: exponent sum - 127, folded into the lane word
@@ -185,15 +191,22 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
       const int ee = (int)(uu[r] & 0x7F800000u);
 #pragma unroll
       for (int t = 0; t < TC; ++t) {
-        const uint32_t v = lds_u8((uu[r] & rmask) | ci[t]);
+        // e = (carry << 23) + (mantissa bits << (23 - m)), AMsimulator.inl:22-23,31
+        uint32_t e;
+        if (GLUT) {
+          const uint32_t v = __ldg(lut_g + ((uu[r] & rmask) | ci[t]));
+          e = v * mult + (v >> 7) * cadj;
+        } else {
+          e = lds_u8((uu[r] & rmask) | ci[t]) * mult;
+        }
         if (EXACT) {
           // bits = sign + ((ea + eb - 127 + carry) << 23) + mantissa, uint32 wrap
-          const uint32_t bits = v * mult + (pp + cs[t]);
+          const uint32_t bits = e + (pp + cs[t]);
           // product is +0 when ea + eb <= 127 (AMsimulator.inl:28); adding +0
           // never changes a non-negative-zero accumulator, so skip the add.
           if (ee > cn[t]) acc[4 * g4 + r][t] = __fadd_rn(acc[4 * g4 + r][t], __uint_as_float(bits));
         } else {
-          const float y = __uint_as_float(v * mult + cs[t]);
+          const float y = __uint_as_float(e + cs[t]);
           const float sacc = __fmaf_rn(__uint_as_float(pp), y, acc[4 * g4 + r][t]);
           acc[4 * g4 + r][t] = nz[t] ? sacc : acc[4 * g4 + r][t];
         }
@@ -230,7 +243,7 @@ struct SmemLayout {
 // -----------------------------------------------------------------------------
 // gather_gemm: V gathered along k.  grid = (ceil(P/BP), ceil(Q/64), batch).
 // -----------------------------------------------------------------------------
-template <int WP, bool EXACT, bool VEC, bool CLUSTER>
+template <int WP, bool EXACT, bool VEC, bool CLUSTER, bool GLUT>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
@@ -253,7 +266,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   float* __restrict__ Og = prm.O + (long long)blockIdx.z * prm.o_bs;
   const Gather& g = prm.g;
 
-  copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+  if (!GLUT) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
 
   // ---- this thread's share of the V tile: 2 rows (p) x 2 groups of 4 k ------
   int pl[2], r0[2], c0[2];
@@ -389,7 +402,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
     const uint32_t* us = Us + buf * BK * US + ucol;
 AMSIM_UNROLL_K
     for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult);
+      mac_step<EXACT, GLUT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+                            prm.lut_raw);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }
@@ -450,7 +464,7 @@ AMSIM_UNROLL_K
 // k in [s * k_chunk, min((s+1) * k_chunk, K)) and writes ws[s] (or O if there
 // is only one split).
 // -----------------------------------------------------------------------------
-template <int WP, bool EXACT, bool VEC>
+template <int WP, bool EXACT, bool VEC, bool GLUT>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
@@ -475,7 +489,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
   const float* __restrict__ Vg = prm.V;
   const float* __restrict__ Ug = prm.U;
 
-  copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+  if (!GLUT) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
 
   // ---- this thread's 4 consecutive p (same for every k row it stages) ---------
   const int pl = 4 * (t % GPR);
@@ -573,7 +587,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
     const uint32_t* us = Us + buf * BK * US + ucol;
 AMSIM_UNROLL_K
     for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult);
+      mac_step<EXACT, GLUT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+                            prm.lut_raw);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }

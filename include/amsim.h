@@ -27,7 +27,10 @@
  *                        < 2^-125); each forward / input-gradient output is one
  *                        ascending-k FP32 chain like the reference kernel, the
  *                        filter / weight gradients are split along the
- *                        reduction and summed in a fixed order.
+ *                        reduction and summed in a fixed order, and so are
+ *                        forward / input-gradient outputs of shapes with too
+ *                        few output tiles to fill the GPU (thread-block clusters
+ *                        share a tile's reduction).  Run-to-run identical.
  *   AMSIM_DETERMINISTIC  every product is the reference primitive bit for bit
  *                        (cuda/AMsimulator.inl:13-36) and every output is one
  *                        ascending chain in the reference's order
@@ -70,7 +73,9 @@ const char* amsim_version(void);
  * op's `mant_mul_lut` attribute: "<MODEL>_<m>.bin", m = digits between the
  * last '_' and the last '.', file = 2^(2m) raw bytes.  Handles are cached per
  * (real path, device) and reference counted; close drops one reference.
- * The file must hold exactly 2^(2m) bytes (the reference reads "up to"). */
+ * The file must hold exactly 2^(2m) bytes (the reference reads "up to").
+ * For m <= 7 the GEMM kernels keep the table in shared memory; for m = 8..11
+ * (up to 4 MiB) they look it up in global memory, where it stays L2-resident. */
 int amsim_lut_open(const char* path, int device, amsim_lut** out);
 /* Same, from bytes already in host memory (m given explicitly). */
 int amsim_lut_open_bytes(const uint8_t* bytes, int m, int device, amsim_lut** out);

@@ -317,10 +317,6 @@ def test_errors_through_the_abi(ops):
     with pytest.raises(_lib.AmsimError) as e:
         ops.denseam(torch.zeros(2, 2, device="cuda"), torch.zeros(2, 2, device="cuda"), "/nonexistent/X_7.bin")
     assert e.value.code == _lib.ERR_LUT_IO
-    if os.path.exists(BIG_LUT):
-        with pytest.raises(_lib.AmsimError) as e:
-            ops.denseam(torch.zeros(2, 2, device="cuda"), torch.zeros(2, 2, device="cuda"), BIG_LUT)
-        assert e.value.code == _lib.ERR_UNSUPPORTED
     # too-small workspace is refused, nothing is launched
     import ctypes as C
     lut = ops.get_lut(lut_path("MBM_7"), "cuda")
@@ -382,3 +378,40 @@ def test_cluster_split_of_the_reduction(ops, oracle, luts, force, monkeypatch):
     assert np.array_equal(y, y2), "rank-ordered combine: run-to-run identical"
     yd = ops.convam(dev(x), dev(wt), deterministic=True, **kw_).cpu().numpy()
     assert_bit_equal(yd, oracle.conv2d_fwd(g, x, wt, lut, m), "deterministic mode ignores the split")
+
+
+@pytest.mark.parametrize("m", [8, 9, 11])
+def test_large_lut_global_memory_path(ops, oracle, m, tmp_path):
+    """m = 8..11: the table (up to 4 MiB) does not fit in shared memory and is
+    looked up in global memory (L2-resident).  Same parity bars.  m = 11 uses
+    the LUT generated from the reference's 32-bit MBM model when it is built,
+    other widths a seeded random table (any byte pattern is a valid LUT)."""
+    rng = np.random.default_rng(40 + m)
+    if m == 11 and os.path.exists(BIG_LUT):
+        from oracle.oracle import load_lut
+        path = BIG_LUT
+        lutb, _ = load_lut(path)
+    else:
+        lutb = rng.integers(0, 256, size=1 << (2 * m), dtype=np.uint8)
+        path = str(tmp_path / f"RAND_{m}.bin")
+        lutb.tofile(path)
+    x, wt = _conv_case(rng, 2, 9, 9, 8, 3, 3, 20)
+    g = oracle.geometry(2, 9, 9, 8, 3, 3, 20, 1, 1, "SAME")
+    dy = rng.standard_normal((2, 9, 9, 20)).astype(np.float32)
+    kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=path)
+    for det in (True, False):
+        chk = assert_bit_equal if det else assert_close
+        chk(ops.convam(dev(x), dev(wt), deterministic=det, **kw_).cpu().numpy(), oracle.conv2d_fwd(g, x, wt, lutb, m), f"m={m} fwd")
+        chk(ops.convam_filter_grad(wt.shape, dev(x), dev(dy), deterministic=det, **kw_).cpu().numpy(),
+            oracle.conv2d_bwd_filter(g, x, dy, lutb, m), f"m={m} fgrad")
+        chk(ops.convam_input_grad(x.shape, dev(wt), dev(dy), deterministic=det, **kw_).cpu().numpy(),
+            oracle.conv2d_bwd_input(g, wt, dy, lutb, m), f"m={m} igrad")
+        a = rng.standard_normal((3, 10, 33)).astype(np.float32)
+        b = rng.standard_normal((3, 33, 7)).astype(np.float32)
+        chk(ops.matmulam(dev(a), dev(b), mant_mul_lut=path, deterministic=det).cpu().numpy(), oracle.matmul(a, b, lutb, m), f"m={m} matmul")
+        xd = rng.standard_normal((9, 21)).astype(np.float32)
+        wd = rng.standard_normal((21, 5)).astype(np.float32)
+        gd = rng.standard_normal((9, 5)).astype(np.float32)
+        dxx, dww = ops.denseam_grad(dev(gd), dev(xd), dev(wd), path, deterministic=det)
+        chk(dxx.cpu().numpy(), oracle.dense_bwd_input(wd, gd, lutb, m), f"m={m} dense dx")
+        chk(dww.cpu().numpy(), oracle.dense_bwd_weight(xd, gd, lutb, m), f"m={m} dense dw")
