@@ -461,7 +461,7 @@ int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x, const f
   g.PH = out_h; g.PW = out_w; g.ps_h = stride_h; g.ps_w = stride_w; g.off_t = pad_top; g.off_l = pad_left;
   g.lim_h = in_h; g.lim_w = in_w; g.dil_h = 1; g.dil_w = 1; g.SH = in_h; g.SW = in_w; g.SC = in_c; g.KW = f_w;
   fill_gather_divs(g);
-  p.taps = f_h * f_w; p.u_flip = 0; p.u_tap = (long long)in_c * out_c; p.u_sk = out_c; p.u_sq = 1;
+  p.u_t0 = 0; p.u_tj = f_w; p.u_ti = 1; p.u_tap = (long long)in_c * out_c; p.u_sk = out_c; p.u_sq = 1;
   p.o_sp = out_c; p.o_sq = 1;
   fill_lut(p, lut, /*v_is_first_operand=*/true);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
@@ -478,20 +478,59 @@ int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, c
   if (!dy || !w || !dx) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   if (out_h == 0 || out_w == 0) return fail(AMSIM_ERR_INVALID, "empty output gradient");
   if (pad_top > f_h - 1 || pad_left > f_w - 1) return fail(AMSIM_ERR_INVALID, "forward padding exceeds filter size - 1");
+  const bool exact = flags & AMSIM_DETERMINISTIC;
+  const int hole_h = (out_h - 1) * stride_h + 1, hole_w = (out_w - 1) * stride_w + 1;  // convam.cc:1066-1067
+  const int bpt = f_h - 1 - pad_top, bpl = f_w - 1 - pad_left;                        // convam.cc:1083-1084
   Params p{};
   p.V = dy; p.U = w; p.O = dx;
-  p.P = batch * in_h * in_w; p.Q = in_c; p.K = f_h * f_w * out_c;
-  Gather& g = p.g;
-  // convam.cc:1066-1067, 1083-1084
-  g.PH = in_h; g.PW = in_w; g.ps_h = 1; g.ps_w = 1; g.off_t = f_h - 1 - pad_top; g.off_l = f_w - 1 - pad_left;
-  g.lim_h = (out_h - 1) * stride_h + 1; g.lim_w = (out_w - 1) * stride_w + 1;
-  g.dil_h = stride_h; g.dil_w = stride_w; g.SH = out_h; g.SW = out_w; g.SC = out_c; g.KW = f_w;
-  fill_gather_divs(g);
-  // flipped filter with in/out channels swapped: element (tap, ko; c)
-  p.taps = f_h * f_w; p.u_flip = 1; p.u_tap = (long long)in_c * out_c; p.u_sk = 1; p.u_sq = out_c;
+  p.Q = in_c;
+  p.u_tap = (long long)in_c * out_c; p.u_sk = 1; p.u_sq = out_c;  // w[tap][c][ko]: element (ko; c)
   p.o_sp = in_c; p.o_sq = 1;
   fill_lut(p, lut, true);
-  return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
+  Gather& g = p.g;
+  g.SH = out_h; g.SW = out_w; g.SC = out_c;
+  if (exact || (stride_h == 1 && stride_w == 1)) {
+    // The reference's formulation: every input position gathers KH x KW taps of the
+    // stride-dilated, back-padded gradient; positions between the strides are zeros
+    // that still go through the multiplier.
+    p.P = batch * in_h * in_w; p.K = f_h * f_w * out_c;
+    g.PH = in_h; g.PW = in_w; g.ps_h = 1; g.ps_w = 1; g.off_t = bpt; g.off_l = bpl;
+    g.lim_h = hole_h; g.lim_w = hole_w; g.dil_h = stride_h; g.dil_w = stride_w; g.KW = f_w;
+    fill_gather_divs(g);
+    // flipped filter with in/out channels swapped
+    p.u_t0 = f_h * f_w - 1; p.u_tj = -f_w; p.u_ti = -1;
+    return launch_gather((cudaStream_t)stream, p, 1, exact, lut->device);
+  }
+  // Fast mode, stride > 1: a product with a structural zero is exactly 0, so each
+  // stride phase (y % sh, x % sw) is computed on its own from the taps that can hit
+  // a gradient sample: kh = kh0 + j * sh.  Same products, same order, no zero work.
+  bool any_empty = false;
+  for (int a = 0; a < stride_h && a < in_h; ++a)
+    for (int b = 0; b < stride_w && b < in_w; ++b) {
+      const int kh0 = (((bpt - a) % stride_h) + stride_h) % stride_h, kw0 = (((bpl - b) % stride_w) + stride_w) % stride_w;
+      if (kh0 >= f_h || kw0 >= f_w) any_empty = true;
+    }
+  if (any_empty || stride_h > in_h || stride_w > in_w)
+    CUDA_TRY(cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)batch * in_h * in_w * in_c, (cudaStream_t)stream));
+  for (int a = 0; a < stride_h && a < in_h; ++a)
+    for (int b = 0; b < stride_w && b < in_w; ++b) {
+      const int kh0 = (((bpt - a) % stride_h) + stride_h) % stride_h, kw0 = (((bpl - b) % stride_w) + stride_w) % stride_w;
+      if (kh0 >= f_h || kw0 >= f_w) continue;  // no tap reaches this phase: stays zero
+      const int nh = (f_h - kh0 + stride_h - 1) / stride_h, nw = (f_w - kw0 + stride_w - 1) / stride_w;
+      const int ra = (a - bpt + kh0) / stride_h, rb = (b - bpl + kw0) / stride_w;  // exact divisions
+      Params q = p;
+      Gather& h = q.g;
+      h.PH = (in_h - a + stride_h - 1) / stride_h; h.PW = (in_w - b + stride_w - 1) / stride_w;
+      h.ps_h = 1; h.ps_w = 1; h.off_t = -ra; h.off_l = -rb; h.lim_h = out_h; h.lim_w = out_w;
+      h.dil_h = 1; h.dil_w = 1; h.KW = nw;
+      fill_gather_divs(h);
+      q.P = batch * h.PH * h.PW; q.K = nh * nw * out_c;
+      q.u_t0 = (f_h - 1 - kh0) * f_w + (f_w - 1 - kw0); q.u_tj = -stride_h * f_w; q.u_ti = -stride_w;
+      q.o_strided = 1; q.o_h = in_h; q.o_w = in_w; q.o_sh = stride_h; q.o_sw = stride_w; q.o_a = a; q.o_b = b;
+      rc = launch_gather((cudaStream_t)stream, q, 1, false, lut->device);
+      if (rc) return rc;
+    }
+  return AMSIM_OK;
 }
 
 size_t amsim_conv2d_bwd_filter_workspace(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c,
@@ -592,7 +631,7 @@ int amsim_dense_fwd(void* stream, const amsim_lut* lut, const float* x, const fl
   p.V = x; p.U = w; p.O = y;
   p.P = batch; p.Q = units; p.K = input_width;
   dense_gather(p.g, input_width);
-  p.taps = 1; p.u_flip = 0; p.u_tap = 0; p.u_sk = units; p.u_sq = 1;
+  p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = units; p.u_sq = 1;
   p.o_sp = units; p.o_sq = 1;
   fill_lut(p, lut, true);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
@@ -611,7 +650,7 @@ int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w, co
   p.V = g_; p.U = w; p.O = dx;
   p.P = batch; p.Q = input_width; p.K = units;
   dense_gather(p.g, units);
-  p.taps = 1; p.u_flip = 0; p.u_tap = 0; p.u_sk = 1; p.u_sq = units;
+  p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = 1; p.u_sq = units;
   p.o_sp = input_width; p.o_sq = 1;
   fill_lut(p, lut, /*v_is_first_operand=*/false);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
@@ -669,7 +708,7 @@ int amsim_matmul(void* stream, const amsim_lut* lut, const float* a, const float
   p.V = a; p.U = b; p.O = c;
   p.P = row_a; p.Q = col_b; p.K = col_a;
   dense_gather(p.g, col_a);
-  p.taps = 1; p.u_flip = 0; p.u_tap = 0; p.u_sk = col_b; p.u_sq = 1;
+  p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = col_b; p.u_sq = 1;
   p.o_sp = col_b; p.o_sq = 1;
   p.v_bs = batch_a > 1 ? (long long)row_a * col_a : 0;
   p.u_bs = batch_b > 1 ? (long long)row_b * col_b : 0;

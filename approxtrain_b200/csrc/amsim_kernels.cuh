@@ -104,11 +104,16 @@ struct Params {
   int P, Q, K;  // extents of p, q and the reduction
   Gather g;
   // U element for reduction index k = tap * g.SC + kk and column q sits at
-  //   U[tap' * u_tap + kk * u_sk + q * u_sq], tap' = taps-1-tap if u_flip
-  // (the flip folds cuda/reverseNswapdim23.cu into the index map).
+  //   U[tap' * u_tap + kk * u_sk + q * u_sq],
+  //   tap' = u_t0 + (tap / g.KW) * u_tj + (tap % g.KW) * u_ti
+  // (negative steps fold the spatial flip of cuda/reverseNswapdim23.cu into the
+  // index map; steps larger than one select the taps of one stride phase).
   long long u_tap;
-  int u_sk, u_sq, u_flip, taps;
-  long long o_sp, o_sq;         // Out[p, q] at O[p * o_sp + q * o_sq]
+  int u_sk, u_sq, u_t0, u_tj, u_ti;
+  long long o_sp, o_sq;         // Out[p, q] at O[row(p) * o_sp + q * o_sq]
+  // row(p) = p, or for a strided output grid (one stride phase of an input
+  // gradient): p -> (n, yy, xx) over g.PH x g.PW, row = (n*o_h + yy*o_sh + o_a)*o_w + xx*o_sw + o_b
+  int o_strided, o_h, o_w, o_sh, o_sw, o_a, o_b;
   long long v_bs, u_bs, o_bs;   // per-blockIdx.z (batch) offsets
   const uint8_t* lut;           // encoded table, rows of `rowstride` bytes
   int lut_bytes;                // multiple of 16
@@ -347,7 +352,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
       if (kglob < prm.K && qg < prm.Q) {
         const uint32_t tap = fdiv((uint32_t)kglob, g.d_sc);
         const int kk = kglob - (int)tap * g.SC;
-        const int tp = prm.u_flip ? prm.taps - 1 - (int)tap : (int)tap;
+        const int tj = (int)fdiv(tap, g.d_kw);
+        const int tp = prm.u_t0 + tj * prm.u_tj + ((int)tap - tj * g.KW) * prm.u_ti;
         val = __ldg(Ug + (long long)tp * prm.u_tap + (long long)kk * prm.u_sk + (long long)qg * prm.u_sq);
       }
       uraw[j] = val;
@@ -441,7 +447,15 @@ AMSIM_UNROLL_K
   for (int c = 0; c < TC; ++c) {
     const int pg = p0 + vcol + c;
     if (pg >= prm.P) continue;
-    float* orow = Og + (long long)pg * prm.o_sp;
+    long long row = pg;
+    if (prm.o_strided) {
+      const uint32_t n = fdiv((uint32_t)pg, g.d_img);
+      const uint32_t rem = (uint32_t)pg - n * (uint32_t)(g.PH * g.PW);
+      const uint32_t yy = fdiv(rem, g.d_pw);
+      const uint32_t xx = rem - yy * (uint32_t)g.PW;
+      row = ((long long)n * prm.o_h + yy * prm.o_sh + prm.o_a) * prm.o_w + xx * prm.o_sw + prm.o_b;
+    }
+    float* orow = Og + row * prm.o_sp;
 #pragma unroll
     for (int g4 = 0; g4 < TR / 4; ++g4) {
       const int qg = q0 + ucol + 4 * g4;
