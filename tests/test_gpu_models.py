@@ -140,3 +140,27 @@ def test_transformer_am_small_step_runs():
     for _ in range(6):
         l1 = float(tr.step(lambda: torch.nn.functional.cross_entropy(net(src, tgt[:, :-1]).reshape(-1, 120), tgt[:, 1:].reshape(-1))))
     assert np.isfinite(l1) and l1 < l0
+
+
+def test_cuda_graph_replay_matches_eager_steps():
+    """The whole train step (ops, split-K reduction, cluster launches, SGD update)
+    is capturable; replaying it gives the eager losses bit for bit."""
+    from approxtrain_b200.nets import LeNet5
+    from approxtrain_b200.dp import DataParallelSGD
+    g = torch.Generator().manual_seed(3)
+    x = torch.rand(64, 28, 28, 1, generator=g).cuda()
+    y = torch.randint(0, 10, (64,), generator=g).cuda()
+
+    def run(graphed):
+        torch.manual_seed(1)
+        net = LeNet5(lut_path("MIT_7")).cuda()
+        tr = DataParallelSGD(net, lr=0.05)
+        fn = lambda: torch.nn.functional.cross_entropy(net(x), y)
+        if not graphed:
+            return [float(tr.step(fn)) for _ in range(3 + 4)]   # capture() runs 3 warm-up steps; recording does not execute
+        replay = tr.capture(fn, warmup=3)
+        return [float(replay()) for _ in range(4)]
+
+    eager = run(False)
+    graph = run(True)
+    assert graph == eager[3:], (graph, eager)
