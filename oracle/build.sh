@@ -5,6 +5,7 @@
 #   oracle/_ref/libref_amsim.so    reference cuda/AMsimulator.inl as host C++
 #   oracle/_ref/lut/*.bin          output of the reference's lut/lut_gen.cc
 #   oracle/_ref/lut/MBM_11.bin     m = 11 LUT from cuda/FPmultMBM_fast32.inl
+#   oracle/_ref/libref_model_<LUT>.so   the functional model each shipped LUT was generated from
 # Reference sources are compiled where they lie; nothing is copied.
 # Usage: oracle/build.sh [reference_dir]   (default /root/reference)
 set -euo pipefail
@@ -26,6 +27,13 @@ if [ -f "$ref/cuda/AMsimulator.inl" ]; then
              MITCHEL10_MULTIPLIER BFLOAT; do
     g++ -w -D$mul -I"$ref/lut" -o "$tmp/lut_gen_$mul" "$ref/lut/lut_gen.cc"
     (cd "$here/_ref/lut" && "$tmp/lut_gen_$mul")
+  done
+  # the functional models themselves, for the LUT-vs-model sweep of lut/test.cc
+  for pair in FMBM16_MULTIPLIER:MBM_7 FMBM14_MULTIPLIER:MBM_5 FMBM12_MULTIPLIER:MBM_3 FMBM10_MULTIPLIER:MBM_1 \
+              MITCHEL16_MULTIPLIER:MIT_7 MITCHEL14_MULTIPLIER:MIT_5 MITCHEL12_MULTIPLIER:MIT_3 \
+              MITCHEL10_MULTIPLIER:MIT_1 BFLOAT:ACC_7; do
+    g++ -w -O1 -fPIC -shared -std=c++14 -D${pair%%:*} -I"$ref/lut" \
+        -o "$here/_ref/libref_model_${pair##*:}.so" "$here/ref_models.cc"
   done
   g++ -w -O1 -D__device__= -I"$ref/cuda" -o "$tmp/gen_lut_m11" "$here/gen_lut_m11.cc"
   "$tmp/gen_lut_m11" "$here/_ref/lut/MBM_11.bin"

@@ -239,3 +239,26 @@ class RefPrimitive:
         out = np.empty_like(at)
         self.lib.ref_am_mul_bits_array(at, bt, out, at.size, lut, m)
         return out
+
+
+class RefModel:
+    """One of the reference's functional multiplier models (the C code a shipped
+    LUT was generated from), built as host code by oracle/build.sh."""
+
+    def __init__(self, lut_name: str):
+        path = os.path.join(_HERE, "_ref", f"libref_model_{lut_name}.so")
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self.lib = C.CDLL(path)
+        self.lib.ref_model_mul_array.argtypes = [_u32p, _u32p, _u32p, C.c_uint64]
+
+    @staticmethod
+    def available(lut_name: str) -> bool:
+        return os.path.exists(os.path.join(_HERE, "_ref", f"libref_model_{lut_name}.so"))
+
+    def mul_bits_array(self, at: np.ndarray, bt: np.ndarray) -> np.ndarray:
+        at = np.ascontiguousarray(at, np.uint32).reshape(-1)
+        bt = np.ascontiguousarray(bt, np.uint32).reshape(-1)
+        out = np.empty_like(at)
+        self.lib.ref_model_mul_array(at, bt, out, at.size)
+        return out

@@ -415,3 +415,51 @@ def test_large_lut_global_memory_path(ops, oracle, m, tmp_path):
         dxx, dww = ops.denseam_grad(dev(gd), dev(xd), dev(wd), path, deterministic=det)
         chk(dxx.cpu().numpy(), oracle.dense_bwd_input(wd, gd, lutb, m), f"m={m} dense dx")
         chk(dww.cpu().numpy(), oracle.dense_bwd_weight(xd, gd, lutb, m), f"m={m} dense dw")
+
+
+# The shape table of the reference's own convolution test (test/convam_final_test.py:167-196), including the
+# four entries its dict literal overwrites: (N, H, W, C, KH, KW, C, K).
+REFERENCE_TEST_SHAPES = [
+    (1, 4, 4, 1, 4, 4, 1, 1), (1, 4, 4, 1, 3, 3, 1, 1), (1, 4, 4, 1, 2, 2, 1, 1), (1, 4, 4, 1, 1, 1, 1, 1),
+    (1, 4, 8, 1, 4, 4, 1, 1), (1, 4, 8, 1, 3, 3, 1, 1), (1, 4, 8, 1, 2, 2, 1, 1), (1, 4, 8, 1, 1, 1, 1, 1),
+    (1, 4, 8, 1, 4, 5, 1, 1), (1, 4, 8, 1, 3, 4, 1, 1), (1, 4, 8, 1, 2, 1, 1, 1),
+    (1, 4, 8, 2, 4, 5, 2, 3), (1, 4, 8, 2, 3, 4, 2, 3), (1, 4, 8, 2, 2, 1, 2, 3), (1, 4, 8, 2, 1, 1, 2, 3),
+    (1, 8, 4, 3, 5, 4, 3, 4), (1, 8, 4, 3, 3, 4, 3, 4), (1, 8, 4, 3, 2, 1, 3, 4), (1, 8, 4, 3, 1, 1, 3, 4),
+    (1, 20, 20, 3, 5, 5, 3, 4), (1, 20, 20, 3, 5, 4, 3, 4), (1, 20, 20, 3, 2, 1, 3, 4), (1, 20, 20, 3, 1, 1, 3, 4),
+    (128, 32, 32, 1, 5, 5, 1, 6), (128, 14, 14, 6, 5, 5, 6, 16), (4, 4, 4, 1, 2, 2, 1, 2), (4, 14, 14, 1, 5, 5, 1, 16),
+]
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_reference_conv_test_matrix(ops, oracle, luts, stride):
+    """Same inputs and acceptance as the reference's test: integers in [-2, 2)
+    (:165-166), forward and both gradients for VALID and SAME compared with the
+    exact convolution, pass if the mean error is <= 1e-7 (:16-17,64) — run with
+    the bf16-exact LUT, the closest LUT to the exact-multiply build that test
+    targets — and additionally bit for bit against the oracle in deterministic mode."""
+    lut, m = luts["ACC_7"]
+    rng = np.random.default_rng(1000 + stride)
+    for shape in REFERENCE_TEST_SHAPES:
+        n, h, w, c, kh, kw, _, k = shape
+        for padding in ("VALID", "SAME"):
+            if padding == "VALID" and (kh > h or kw > w):
+                continue
+            x = rng.integers(-2, 2, size=(n, h, w, c)).astype(np.float32)
+            wt = rng.integers(-2, 2, size=(kh, kw, c, k)).astype(np.float32)
+            g = oracle.geometry(n, h, w, c, kh, kw, k, stride, stride, padding)
+            dy = rng.integers(-2, 2, size=(n, g.out_h, g.out_w, k)).astype(np.float32)
+            kw_ = dict(strides=[1, stride, stride, 1], padding=padding, mant_mul_lut=lut_path("ACC_7"))
+            exact = (oracle.cpu_conv2d_fwd(g, x, wt), oracle.cpu_conv2d_bwd_filter(g, x, dy), oracle.cpu_conv2d_bwd_input(g, wt, dy))
+            for det in (False, True):
+                got = (ops.convam(dev(x), dev(wt), deterministic=det, **kw_).cpu().numpy(),
+                       ops.convam_filter_grad(wt.shape, dev(x), dev(dy), deterministic=det, **kw_).cpu().numpy(),
+                       ops.convam_input_grad(x.shape, dev(wt), dev(dy), deterministic=det, **kw_).cpu().numpy())
+                for a, b, what in zip(got, exact, ("fwd", "filter-grad", "input-grad")):
+                    assert np.abs(a - b).mean() <= 1e-7, (shape, padding, what, det)
+                if det:
+                    assert_bit_equal(got[0], oracle.conv2d_fwd(g, x, wt, lut, m), f"{shape} {padding} fwd")
+                    assert_bit_equal(got[1], oracle.conv2d_bwd_filter(g, x, dy, lut, m), f"{shape} {padding} fgrad")
+                    assert_bit_equal(got[2], oracle.conv2d_bwd_input(g, wt, dy, lut, m), f"{shape} {padding} igrad")
+                else:
+                    for a, b in zip(got, exact):
+                        assert np.array_equal(a, b)   # integer products and sums are exact in fast mode

@@ -240,3 +240,35 @@ def test_cpu_baseline_loops_agree_with_each_other(oracle):
     s = float((y.astype(np.float64) * dy).sum())
     assert abs(float((w.astype(np.float64) * dw).sum()) - s) < 1e-3 * abs(s)
     assert abs(float((x.astype(np.float64) * dx).sum()) - s) < 1e-3 * abs(s)
+
+
+@pytest.mark.parametrize("name", SMALL_LUTS)
+def test_lut_primitive_vs_functional_model_sweep(oracle, luts, name):
+    """The reference's own LUT check (lut/test.cc:70-101): sweep operands whose
+    mantissas carry only the top m bits, compare AMsimulator(LUT) with the
+    functional C model the LUT was generated from, skipping pairs with a zero
+    exponent field (:84) as that test does.  Where the product is a normal
+    number the two must agree bit for bit; outside that range the model clamps
+    (subnormal -> 0, overflow -> inf) while the simulator's exponent wraps."""
+    from oracle.oracle import RefModel
+    if not RefModel.available(name):
+        pytest.skip("oracle/_ref not built (no reference checkout on this machine)")
+    model = RefModel(name)
+    lut, m = luts[name]
+    rng = np.random.default_rng(99)
+    n = 400_000
+    ea = rng.integers(1, 255, size=n, dtype=np.uint32)
+    eb = rng.integers(1, 255, size=n, dtype=np.uint32)
+    ma = rng.integers(0, 1 << m, size=n, dtype=np.uint32) << np.uint32(23 - m)
+    mb = rng.integers(0, 1 << m, size=n, dtype=np.uint32) << np.uint32(23 - m)
+    sa = rng.integers(0, 2, size=n, dtype=np.uint32) << np.uint32(31)
+    sb = rng.integers(0, 2, size=n, dtype=np.uint32) << np.uint32(31)
+    at, bt = sa | (ea << np.uint32(23)) | ma, sb | (eb << np.uint32(23)) | mb
+    got = oracle.mul(at.view(np.float32), bt.view(np.float32), lut, m).view(np.uint32)
+    want = model.mul_bits_array(at, bt)
+    # result exponent of the simulator: ea + eb - 127 + carry must be a normal exponent
+    e_sum = ea.astype(np.int64) + eb.astype(np.int64) - 127
+    normal = (e_sum >= 2) & (e_sum <= 252)
+    assert normal.sum() > n // 4
+    mism = (got != want) & normal
+    assert not mism.any(), f"{name}: {mism.sum()} mismatches in the normal range, first at {np.argwhere(mism)[0]}"
