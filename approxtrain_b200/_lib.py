@@ -14,6 +14,7 @@ OK = 0
 ERR_INVALID, ERR_LUT_NAME, ERR_LUT_IO, ERR_LUT_SIZE, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED = range(1, 8)
 FAST = 0
 DETERMINISTIC = 1
+INT32 = 2
 STATIC_SCRATCH_BYTES = 8 << 20
 
 # every symbol include/amsim.h declares

@@ -138,7 +138,7 @@ int upload_lut(const uint8_t* bytes, int m, int device, amsim_lut** out) {
 
 int check_common(const amsim_lut* lut, unsigned flags, bool need_gemm) {
   if (!lut) return fail(AMSIM_ERR_INVALID, "lut handle is NULL");
-  if (flags & ~AMSIM_DETERMINISTIC) return fail(AMSIM_ERR_INVALID, "unknown flag bits 0x%x", flags);
+  if (flags & ~(AMSIM_DETERMINISTIC | AMSIM_INT32)) return fail(AMSIM_ERR_INVALID, "unknown flag bits 0x%x", flags);
   (void)need_gemm;
   int dev = -1;
   CUDA_TRY(cudaGetDevice(&dev));
@@ -172,6 +172,7 @@ void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
   p.cmask = (1u << lut->m) - 1u;
   p.cadj = (1u << 23) - 128u * p.mult;
   p.lut_raw = v_is_first_operand ? lut->d_raw_t : lut->d_raw;
+  p.v_first = v_is_first_operand ? 1 : 0;
   uint32_t al = 16;
   while (al < (uint32_t)lut->enc_bytes) al <<= 1;
   p.lut_align = al;  // m > 7: no table in shared memory (enc_bytes = 0)
@@ -316,6 +317,20 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
     else       { if (vec) AMSIM_GO(false, true, false); else AMSIM_GO(false, false, false); }
   }
 #undef AMSIM_GO
+}
+
+// T = int32: one thread per output on the raw table (see naive_*_i32).
+int launch_naive_i32(cudaStream_t st, Params& p, const amsim_lut* lut, bool fgrad) {
+  if (p.P <= 0 || p.Q <= 0) return AMSIM_OK;
+  p.lut_raw = lut->d_raw;  // rows by the first operand; v_first tells the kernel which operand that is
+  const long long n = (long long)p.P * p.Q;
+  const unsigned blocks = (unsigned)((n + 127) / 128);
+  if (fgrad)
+    naive_fgrad_i32<<<blocks, 128, 0, st>>>(p);
+  else
+    naive_gather_i32<<<blocks, 128, 0, st>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  return AMSIM_OK;
 }
 
 int check_conv_dims(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w,
@@ -464,6 +479,7 @@ int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x, const f
   p.u_t0 = 0; p.u_tj = f_w; p.u_ti = 1; p.u_tap = (long long)in_c * out_c; p.u_sk = out_c; p.u_sq = 1;
   p.o_sp = out_c; p.o_sq = 1;
   fill_lut(p, lut, /*v_is_first_operand=*/true);
+  if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, false);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
 }
 
@@ -478,7 +494,8 @@ int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, c
   if (!dy || !w || !dx) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   if (out_h == 0 || out_w == 0) return fail(AMSIM_ERR_INVALID, "empty output gradient");
   if (pad_top > f_h - 1 || pad_left > f_w - 1) return fail(AMSIM_ERR_INVALID, "forward padding exceeds filter size - 1");
-  const bool exact = flags & AMSIM_DETERMINISTIC;
+  const bool i32 = flags & AMSIM_INT32;
+  const bool exact = (flags & AMSIM_DETERMINISTIC) || i32;  // int32 uses the reference's dense formulation
   const int hole_h = (out_h - 1) * stride_h + 1, hole_w = (out_w - 1) * stride_w + 1;  // convam.cc:1066-1067
   const int bpt = f_h - 1 - pad_top, bpl = f_w - 1 - pad_left;                        // convam.cc:1083-1084
   Params p{};
@@ -499,6 +516,7 @@ int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, c
     fill_gather_divs(g);
     // flipped filter with in/out channels swapped
     p.u_t0 = f_h * f_w - 1; p.u_tj = -f_w; p.u_ti = -1;
+    if (i32) return launch_naive_i32((cudaStream_t)stream, p, lut, false);
     return launch_gather((cudaStream_t)stream, p, 1, exact, lut->device);
   }
   // Fast mode, stride > 1: a product with a structural zero is exactly 0, so each
@@ -537,6 +555,7 @@ size_t amsim_conv2d_bwd_filter_workspace(int batch, int in_h, int in_w, int in_c
                                          int out_h, int out_w, unsigned flags) {
   (void)in_h; (void)in_w;
   if (batch <= 0 || in_c <= 0 || f_h <= 0 || f_w <= 0 || out_c <= 0 || out_h <= 0 || out_w <= 0) return 0;
+  if (flags & AMSIM_INT32) return 0;
   return plan_fgrad(f_h * f_w * in_c, out_c, batch * out_h * out_w, flags & AMSIM_DETERMINISTIC).ws_bytes;
 }
 
@@ -564,6 +583,7 @@ int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, 
   fill_gather_divs(g);
   p.u_sk = out_c; p.u_sq = 1;
   fill_lut(p, lut, true);
+  if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, true);
   return launch_fgrad((cudaStream_t)stream, p, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
 }
 
@@ -634,6 +654,7 @@ int amsim_dense_fwd(void* stream, const amsim_lut* lut, const float* x, const fl
   p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = units; p.u_sq = 1;
   p.o_sp = units; p.o_sq = 1;
   fill_lut(p, lut, true);
+  if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, false);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
 }
 
@@ -653,11 +674,13 @@ int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w, co
   p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = 1; p.u_sq = units;
   p.o_sp = input_width; p.o_sq = 1;
   fill_lut(p, lut, /*v_is_first_operand=*/false);
+  if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, false);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
 }
 
 size_t amsim_dense_bwd_weight_workspace(int batch, int units, int input_width, unsigned flags) {
   if (batch <= 0 || units <= 0 || input_width <= 0) return 0;
+  if (flags & AMSIM_INT32) return 0;
   return plan_fgrad(input_width, units, batch, flags & AMSIM_DETERMINISTIC).ws_bytes;
 }
 
@@ -683,6 +706,7 @@ int amsim_dense_bwd_weight(void* stream, const amsim_lut* lut, const float* x, c
   fill_gather_divs(g);
   p.u_sk = units; p.u_sq = 1;
   fill_lut(p, lut, true);
+  if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, true);
   return launch_fgrad((cudaStream_t)stream, p, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
 }
 
@@ -692,6 +716,8 @@ int amsim_matmul(void* stream, const amsim_lut* lut, const float* a, const float
   if (rc) return rc;
   if (batch_a < 0 || batch_b < 0 || row_a < 0 || col_a < 0 || row_b < 0 || col_b < 0)
     return fail(AMSIM_ERR_INVALID, "negative matrix dimension");
+  if (flags & AMSIM_INT32)
+    return fail(AMSIM_ERR_UNSUPPORTED, "MatMulAM is registered for float only (matmulam.cc:269-274)");
   if (col_a != row_b) return fail(AMSIM_ERR_INVALID, "Does not meet cols of mat a is equal rows of mat b");
   if (batch_a > 1 && batch_b > 1 && batch_a != batch_b)
     return fail(AMSIM_ERR_INVALID, "Does not meet batch of mat a is equal batch of matb");

@@ -129,6 +129,7 @@ struct Params {
   // combine their register tiles through distributed shared memory (1 = no split)
   int ksplit;
   int tile_bytes;               // bytes reserved before the table (operand tiles, or the exchange buffer)
+  int v_first;                  // the lane operand V is the multiplier's first operand (int32 kernels)
   // fgrad only
   int k_chunk, splits;
   float* ws;                    // [splits][P][Q] partial sums when splits > 1
@@ -647,6 +648,75 @@ __device__ __forceinline__ uint32_t am_mul_bits(uint32_t at, uint32_t bt, const 
   const uint32_t e = ((at >> 23) & 0xFFu) + ((bt >> 23) & 0xFFu);
   if (e <= 127u) return 0u;
   return ((at ^ bt) & 0x80000000u) + ((e - 127u + (v >> 7)) << 23) + ((v & 0x7Fu) << (23 - m));
+}
+
+// ---- T = int32 ------------------------------------------------------------------
+// The reference also instantiates its kernels for int32 (cuda/gemm.cu:64-67,
+// cuda/denseam_kernel.cu:146-151): operands are converted to float for the
+// multiplier and the accumulator is updated as acc = (int)((float)acc + product)
+// at every step.  Kept for interface completeness: one thread per output, raw
+// table in global memory, no tiling.  Same index maps as the FP32 kernels.
+__device__ __forceinline__ int step_i32(int acc, int a, int b, bool a_first, const uint8_t* __restrict__ lut, int m) {
+  const uint32_t at = __float_as_uint(__int2float_rn(a_first ? a : b));
+  const uint32_t bt = __float_as_uint(__int2float_rn(a_first ? b : a));
+  return __float2int_rz(__fadd_rn(__int2float_rn(acc), __uint_as_float(am_mul_bits(at, bt, lut, m))));
+}
+
+__global__ void naive_gather_i32(const Params prm) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)prm.P * prm.Q) return;
+  const Gather& g = prm.g;
+  const int* __restrict__ V = reinterpret_cast<const int*>(prm.V);
+  const int* __restrict__ U = reinterpret_cast<const int*>(prm.U);
+  const uint32_t p = (uint32_t)(idx / prm.Q);
+  const int q = (int)(idx - (long long)p * prm.Q);
+  const uint32_t n = fdiv(p, g.d_img);
+  const uint32_t rem = p - n * (uint32_t)(g.PH * g.PW);
+  const uint32_t a = fdiv(rem, g.d_pw), b = rem - a * (uint32_t)g.PW;
+  const int r0 = (int)a * g.ps_h - g.off_t, c0 = (int)b * g.ps_w - g.off_l;
+  const long long nb = (long long)n * ((long long)g.SH * g.SW * g.SC);
+  int acc = 0;
+  for (int k = 0; k < prm.K; ++k) {
+    const uint32_t tap = fdiv((uint32_t)k, g.d_sc);
+    const int ch = k - (int)tap * g.SC;
+    const int kh = (int)fdiv(tap, g.d_kw), kw = (int)tap - kh * g.KW;
+    const int u = r0 + kh, v = c0 + kw;
+    int av = 0;
+    if ((unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
+      const int row = (int)fdiv((uint32_t)u, g.d_dh), col = (int)fdiv((uint32_t)v, g.d_dw);
+      if (row * g.dil_h == u && col * g.dil_w == v) av = V[nb + ((long long)(row * g.SW + col) * g.SC + ch)];
+    }
+    const int tp = prm.u_t0 + kh * prm.u_tj + kw * prm.u_ti;
+    const int bv = U[(long long)tp * prm.u_tap + (long long)ch * prm.u_sk + (long long)q * prm.u_sq];
+    acc = step_i32(acc, av, bv, prm.v_first != 0, prm.lut_raw, prm.m);
+  }
+  reinterpret_cast<int*>(prm.O)[(long long)p * prm.o_sp + (long long)q * prm.o_sq] = acc;
+}
+
+__global__ void naive_fgrad_i32(const Params prm) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)prm.P * prm.Q) return;
+  const Gather& g = prm.g;
+  const int* __restrict__ V = reinterpret_cast<const int*>(prm.V);
+  const int* __restrict__ U = reinterpret_cast<const int*>(prm.U);
+  const uint32_t p = (uint32_t)(idx / prm.Q);
+  const int q = (int)(idx - (long long)p * prm.Q);
+  const uint32_t tap = fdiv(p, g.d_sc);
+  const int ch = (int)(p - tap * (uint32_t)g.SC);
+  const int kh = (int)fdiv(tap, g.d_kw), kw = (int)tap - kh * g.KW;
+  int acc = 0;
+  for (int pix = 0; pix < prm.K; ++pix) {
+    const uint32_t n = fdiv((uint32_t)pix, g.d_img);
+    const uint32_t rem = (uint32_t)pix - n * (uint32_t)(g.PH * g.PW);
+    const uint32_t a = fdiv(rem, g.d_pw), b = rem - a * (uint32_t)g.PW;
+    const int u = (int)a * g.ps_h - g.off_t + kh, v = (int)b * g.ps_w - g.off_l + kw;
+    int av = 0;
+    if ((unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
+      av = V[(long long)n * ((long long)g.SH * g.SW * g.SC) + ((long long)(u * g.SW + v) * g.SC + ch)];
+    const int bv = U[(long long)pix * prm.u_sk + (long long)q * prm.u_sq];
+    acc = step_i32(acc, av, bv, prm.v_first != 0, prm.lut_raw, prm.m);
+  }
+  reinterpret_cast<int*>(prm.O)[(long long)p * prm.Q + q] = acc;
 }
 
 __global__ void mul_elementwise(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,

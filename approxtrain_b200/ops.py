@@ -90,9 +90,17 @@ def _prep(t: torch.Tensor, name: str) -> torch.Tensor:
         raise TypeError(f"{name} must be a torch.Tensor")
     if not t.is_cuda:
         raise ValueError(f"{name} must live on a CUDA device: the AM ops have no CPU implementation")
-    if t.dtype != torch.float32:
-        raise TypeError(f"{name} must be float32, got {t.dtype}")
+    if t.dtype not in (torch.float32, torch.int32):
+        raise TypeError(f"{name} must be float32 or int32 (attr T of the reference ops), got {t.dtype}")
     return t.contiguous()
+
+
+def _dtype_flag(*tensors) -> int:
+    """T: {float, int32} — all tensors of a call share the type."""
+    dts = {t.dtype for t in tensors}
+    if len(dts) != 1:
+        raise TypeError(f"all tensors of an op must have the same dtype, got {sorted(str(d) for d in dts)}")
+    return _lib.INT32 if dts.pop() == torch.int32 else 0
 
 
 def _stream() -> C.c_void_p:
@@ -156,6 +164,8 @@ def am_multiply(a: torch.Tensor, b: torch.Tensor, mant_mul_lut: str) -> torch.Te
     a, b = _prep(a, "a"), _prep(b, "b")
     if a.shape != b.shape:
         raise ValueError("a and b must have the same shape")
+    if a.dtype != torch.float32 or b.dtype != torch.float32:
+        raise TypeError("am_multiply takes float32 tensors")
     lut = get_lut(mant_mul_lut, a.device)
     out = torch.empty_like(a)
     with torch.cuda.device(a.device):
@@ -180,10 +190,10 @@ def convam(input: torch.Tensor, filter: torch.Tensor, strides=None, padding="VAL
     sh, sw = _hw(strides, "strides")
     oh, ow, pt, pl = conv2d_geometry(h, wd, kh, kw, sh, sw, padding)
     lut = get_lut(mant_mul_lut, x.device)
-    y = torch.empty((n, oh, ow, k), dtype=torch.float32, device=x.device)
+    y = torch.empty((n, oh, ow, k), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         check(lib.amsim_conv2d_fwd(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(y), n, h, wd, c, kh, kw, k, oh, ow,
-                                   sh, sw, pt, pl, _flags(deterministic)))
+                                   sh, sw, pt, pl, _flags(deterministic) | _dtype_flag(x, w)))
     return y
 
 
@@ -202,12 +212,12 @@ def convam_input_grad(input_sizes: Sequence[int], filter: torch.Tensor, out_back
     if tuple(dy.shape) != (n, oh, ow, k) or ci != c:
         raise ValueError(f"out_backprop shape {list(dy.shape)} does not match the forward output {[n, oh, ow, k]}")
     lut = get_lut(mant_mul_lut, dy.device)
-    dx = torch.empty((n, h, wd, c), dtype=torch.float32, device=dy.device)
+    dx = torch.empty((n, h, wd, c), dtype=dy.dtype, device=dy.device)
     if dx.numel() == 0:
         return dx
     with torch.cuda.device(dy.device):
         check(lib.amsim_conv2d_bwd_input(_stream(), lut.handle, _ptr(w), _ptr(dy), _ptr(dx), n, h, wd, c, kh, kw, k,
-                                         oh, ow, sh, sw, pt, pl, _flags(deterministic)))
+                                         oh, ow, sh, sw, pt, pl, _flags(deterministic) | _dtype_flag(w, dy)))
     return dx
 
 
@@ -226,10 +236,10 @@ def convam_filter_grad(filter_sizes: Sequence[int], input: torch.Tensor, out_bac
     if tuple(dy.shape) != (n, oh, ow, k) or ci != c:
         raise ValueError(f"out_backprop shape {list(dy.shape)} does not match the forward output {[n, oh, ow, k]}")
     lut = get_lut(mant_mul_lut, x.device)
-    dw = torch.empty((kh, kw, c, k), dtype=torch.float32, device=x.device)
+    dw = torch.empty((kh, kw, c, k), dtype=x.dtype, device=x.device)
     if dw.numel() == 0:
         return dw
-    fl = _flags(deterministic)
+    fl = _flags(deterministic) | _dtype_flag(x, dy)
     ws_bytes = lib.amsim_conv2d_bwd_filter_workspace(n, h, wd, c, kh, kw, k, oh, ow, fl)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
     with torch.cuda.device(x.device):
@@ -248,9 +258,10 @@ def denseam(input: torch.Tensor, weights: torch.Tensor, mant_mul_lut: str = "",
         raise ValueError(f"input width {kin} does not match weights rows {w.shape[0]}")
     u = w.shape[1]
     lut = get_lut(mant_mul_lut, x.device)
-    y = torch.empty((b, u), dtype=torch.float32, device=x.device)
+    y = torch.empty((b, u), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
-        check(lib.amsim_dense_fwd(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(y), b, u, kin, _flags(deterministic)))
+        check(lib.amsim_dense_fwd(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(y), b, u, kin,
+                                  _flags(deterministic) | _dtype_flag(x, w)))
     return y
 
 
@@ -263,7 +274,7 @@ def denseam_grad(grad: torch.Tensor, input: torch.Tensor, weights: torch.Tensor,
     if tuple(g.shape) != (b, u) or w.shape[0] != kin:
         raise ValueError("grad / input / weights shapes are inconsistent")
     lut = get_lut(mant_mul_lut, x.device)
-    fl = _flags(deterministic)
+    fl = _flags(deterministic) | _dtype_flag(g, x, w)
     dx = torch.empty_like(x)
     dw = torch.empty_like(w)
     ws_bytes = lib.amsim_dense_bwd_weight_workspace(b, u, kin, fl)
@@ -287,6 +298,8 @@ def matmulam(a: torch.Tensor, b: torch.Tensor, transpose_a: bool = False, transp
     if transpose_b:
         b = b.transpose(-1, -2)
     a, b = _prep(a, "a"), _prep(b, "b")
+    if a.dtype != torch.float32 or b.dtype != torch.float32:
+        raise TypeError("MatMulAM is registered for float only")
     if a.dim() not in (2, 3) or b.dim() not in (2, 3):
         raise ValueError("Input a and b should be 2 dimensional or 3 dimensional and compitable batch size")
     ba = a.shape[0] if a.dim() == 3 else 0

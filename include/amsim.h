@@ -58,6 +58,13 @@ extern "C" {
 
 #define AMSIM_FAST 0u
 #define AMSIM_DETERMINISTIC 1u
+/* Tensors are int32 instead of float (the reference registers Convam*, Denseam*
+ * for T in {float, int32}: convam.cc:604-621, denseam.cc:126-143).  Pass the
+ * int32 pointers through the float* parameters.  Semantics of the reference's
+ * int32 kernels (cuda/gemm.cu:49,64-67): operands converted to float for the
+ * multiplier, accumulator updated as (int)((float)acc + product) per step.
+ * Unoptimised (one thread per output); implies the reference's order. */
+#define AMSIM_INT32 2u
 
 typedef struct amsim_lut amsim_lut; /* opaque, immutable after open */
 

@@ -12,6 +12,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <limits.h>
 
 #ifdef _OPENMP
 #include <omp.h>
@@ -297,6 +298,103 @@ void am_matmul(const float* a, const float* b, float* c, int batch_a,
   for (int i = 0; i < nb; ++i)
     am_gemm(row_a, col_b, col_a, a + i * sa, col_a, b + i * sb, col_b,
             c + (size_t)i * row_a * col_b, col_b, lut, m);
+}
+
+/* ---------------- T = int32 ------------------------------------------------ */
+
+/* float -> int32 as the GPU's cvt.rzi.s32.f32 does it: truncate, saturate, NaN -> 0 */
+static inline int32_t f2i_sat(float f) {
+  if (f != f) return 0;
+  if (f >= 2147483648.0f) return INT32_MAX;
+  if (f <= -2147483648.0f) return INT32_MIN;
+  return (int32_t)f;
+}
+
+/* one accumulation step of gemm<int32> (cuda/gemm.cu:49 with T = int32) */
+static inline int32_t step_i32(int32_t acc, int32_t a, int32_t b, const uint8_t* lut, int m) {
+  return f2i_sat((float)acc + am_mul((float)a, (float)b, lut, m));
+}
+
+void am_gemm_i32(int m, int n, int k, const int32_t* A, int lda, const int32_t* B,
+                 int ldb, int32_t* C, int ldc, const uint8_t* lut, int mw) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int i = 0; i < m; ++i)
+    for (int j = 0; j < n; ++j) {
+      int32_t acc = 0;
+      for (int l = 0; l < k; ++l) acc = step_i32(acc, A[(size_t)i * lda + l], B[(size_t)l * ldb + j], lut, mw);
+      C[(size_t)i * ldc + j] = acc;
+    }
+}
+
+void am_conv2d_fwd_i32(const am_conv_geom_t* g, const int32_t* x, const int32_t* w,
+                       int32_t* y, const uint8_t* lut, int m) {
+  const int N = g->batch, H = g->in_h, W = g->in_w, C = g->in_c;
+  const int KH = g->f_h, KW = g->f_w, K = g->out_c, OH = g->out_h, OW = g->out_w;
+#pragma omp parallel for collapse(3) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int oh = 0; oh < OH; ++oh)
+      for (int ow = 0; ow < OW; ++ow)
+        for (int ko = 0; ko < K; ++ko) {
+          int32_t acc = 0;
+          for (int kh = 0; kh < KH; ++kh)
+            for (int kw = 0; kw < KW; ++kw) {
+              const int ih = oh * g->stride_h - g->pad_top + kh, iw = ow * g->stride_w - g->pad_left + kw;
+              const int inside = ih >= 0 && iw >= 0 && ih < H && iw < W;
+              for (int c = 0; c < C; ++c) {
+                const int32_t a = inside ? x[(((size_t)n * H + ih) * W + iw) * C + c] : 0;
+                acc = step_i32(acc, a, w[(((size_t)kh * KW + kw) * C + c) * K + ko], lut, m);
+              }
+            }
+          y[(((size_t)n * OH + oh) * OW + ow) * K + ko] = acc;
+        }
+}
+
+void am_conv2d_bwd_filter_i32(const am_conv_geom_t* g, const int32_t* x,
+                              const int32_t* dy, int32_t* dw, const uint8_t* lut, int m) {
+  const int N = g->batch, H = g->in_h, W = g->in_w, C = g->in_c;
+  const int KH = g->f_h, KW = g->f_w, K = g->out_c, OH = g->out_h, OW = g->out_w;
+#pragma omp parallel for collapse(3) schedule(static)
+  for (int kh = 0; kh < KH; ++kh)
+    for (int kw = 0; kw < KW; ++kw)
+      for (int c = 0; c < C; ++c)
+        for (int ko = 0; ko < K; ++ko) {
+          int32_t acc = 0;
+          for (int n = 0; n < N; ++n)
+            for (int oh = 0; oh < OH; ++oh)
+              for (int ow = 0; ow < OW; ++ow) {
+                const int ih = oh * g->stride_h + kh - g->pad_top, iw = ow * g->stride_w + kw - g->pad_left;
+                const int inside = ih >= 0 && iw >= 0 && ih < H && iw < W;
+                const int32_t a = inside ? x[(((size_t)n * H + ih) * W + iw) * C + c] : 0;
+                acc = step_i32(acc, a, dy[(((size_t)n * OH + oh) * OW + ow) * K + ko], lut, m);
+              }
+          dw[(((size_t)kh * KW + kw) * C + c) * K + ko] = acc;
+        }
+}
+
+void am_conv2d_bwd_input_i32(const am_conv_geom_t* g, const int32_t* w,
+                             const int32_t* dy, int32_t* dx, const uint8_t* lut, int m) {
+  const int N = g->batch, H = g->in_h, W = g->in_w, C = g->in_c;
+  const int KH = g->f_h, KW = g->f_w, K = g->out_c, OH = g->out_h, OW = g->out_w;
+  const int sh = g->stride_h, sw = g->stride_w;
+  const int hole_h = (OH - 1) * sh + 1, hole_w = (OW - 1) * sw + 1;
+  const int bpt = KH - 1 - g->pad_top, bpl = KW - 1 - g->pad_left;
+#pragma omp parallel for collapse(3) schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int yy = 0; yy < H; ++yy)
+      for (int xx = 0; xx < W; ++xx)
+        for (int c = 0; c < C; ++c) {
+          int32_t acc = 0;
+          for (int kh = 0; kh < KH; ++kh)
+            for (int kw = 0; kw < KW; ++kw) {
+              const int u = yy - bpt + kh, v = xx - bpl + kw;
+              const int hit = u >= 0 && v >= 0 && u < hole_h && v < hole_w && (u % sh) == 0 && (v % sw) == 0;
+              for (int ko = 0; ko < K; ++ko) {
+                const int32_t a = hit ? dy[(((size_t)n * OH + u / sh) * OW + v / sw) * K + ko] : 0;
+                acc = step_i32(acc, a, w[((((size_t)(KH - 1 - kh)) * KW + (KW - 1 - kw)) * C + c) * K + ko], lut, m);
+              }
+            }
+          dx[(((size_t)n * H + yy) * W + xx) * C + c] = acc;
+        }
 }
 
 /* ---------------- reference CPU op path: exact multiply ------------------ */

@@ -9,7 +9,7 @@
  * the benchmark's CPU-baseline leg do.
  *
  * Parity pin: am_mul_bits() is compared exhaustively against the reference's
- * own cuda/AMsimulator.inl (compiled as host C++ by oracle/build_ref.sh) and
+ * own cuda/AMsimulator.inl (compiled as host C++ by oracle/build.sh) and
  * the LUT bytes against lut/lut_gen.cc output and the shipped lut/ *.bin md5s.
  */
 #ifndef AMSIM_ORACLE_H_
@@ -91,6 +91,20 @@ void am_dense_bwd_input(const float* w, const float* g, float* dx, int batch,
 void am_matmul(const float* a, const float* b, float* c, int batch_a,
                int batch_b, int row_a, int col_a, int col_b, const uint8_t* lut,
                int m);
+
+/* ---- T = int32 (cuda/gemm.cu:64-67, cuda/denseam_kernel.cu:146-151) ---------
+ * The reference instantiates its kernels for int32 as well: operands are
+ * converted to float for the multiplier and the int32 accumulator is updated
+ * as  acc = (int32)((float)acc + product)  at every step (float -> int
+ * conversion truncates toward zero and, on the GPU, saturates; NaN -> 0). */
+void am_gemm_i32(int m, int n, int k, const int32_t* A, int lda, const int32_t* B,
+                 int ldb, int32_t* C, int ldc, const uint8_t* lut, int mw);
+void am_conv2d_fwd_i32(const am_conv_geom_t* g, const int32_t* x, const int32_t* w,
+                       int32_t* y, const uint8_t* lut, int m);
+void am_conv2d_bwd_filter_i32(const am_conv_geom_t* g, const int32_t* x,
+                              const int32_t* dy, int32_t* dw, const uint8_t* lut, int m);
+void am_conv2d_bwd_input_i32(const am_conv_geom_t* g, const int32_t* w,
+                             const int32_t* dy, int32_t* dx, const uint8_t* lut, int m);
 
 /* ---- reference CPU op path (exact multiply), the timed baseline ---------- */
 /* convam.cc:452-491 */

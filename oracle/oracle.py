@@ -99,6 +99,10 @@ class Oracle:
         L.am_matmul.argtypes = [_f32p, _f32p, _f32p] + [C.c_int] * 5 + [_u8p, C.c_int]
         L.cpu_gemm.argtypes = [C.c_int] * 3 + [_f32p, C.c_int, _f32p, C.c_int, _f32p, C.c_int]
         L.am_oracle_set_threads.argtypes = [C.c_int]
+        i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+        L.am_gemm_i32.argtypes = [C.c_int] * 3 + [i32p, C.c_int, i32p, C.c_int, i32p, C.c_int, _u8p, C.c_int]
+        for name in ("am_conv2d_fwd_i32", "am_conv2d_bwd_filter_i32", "am_conv2d_bwd_input_i32"):
+            getattr(L, name).argtypes = [C.POINTER(_Geom), i32p, i32p, i32p, _u8p, C.c_int]
 
     # -- primitive ---------------------------------------------------------
     def mul_bits(self, at: int, bt: int, lut: np.ndarray, m: int) -> int:
@@ -175,6 +179,24 @@ class Oracle:
         nb = max(ba, bb)
         out = np.empty((nb, M, N) if nb else (M, N), np.float32)
         self.lib.am_matmul(_flat(a), _flat(b), out.reshape(-1), ba, bb, M, K, N, lut, m)
+        return out
+
+    # -- T = int32 ----------------------------------------------------------
+    def gemm_i32(self, A, B, lut, m):
+        A = np.ascontiguousarray(A, np.int32)
+        B = np.ascontiguousarray(B, np.int32)
+        out = np.empty((A.shape[0], B.shape[1]), np.int32)
+        self.lib.am_gemm_i32(A.shape[0], B.shape[1], A.shape[1], A.reshape(-1), A.shape[1],
+                             B.reshape(-1), B.shape[1], out.reshape(-1), B.shape[1], lut, m)
+        return out
+
+    def conv2d_i32(self, which, g: ConvGeom, p, q, lut, m):
+        shape = {"fwd": (g.batch, g.out_h, g.out_w, g.out_c), "bwd_filter": (g.f_h, g.f_w, g.in_c, g.out_c),
+                 "bwd_input": (g.batch, g.in_h, g.in_w, g.in_c)}[which]
+        out = np.empty(shape, np.int32)
+        gc = g._c()
+        getattr(self.lib, f"am_conv2d_{which}_i32")(C.byref(gc), np.ascontiguousarray(p, np.int32).reshape(-1),
+                                                    np.ascontiguousarray(q, np.int32).reshape(-1), out.reshape(-1), lut, m)
         return out
 
     # -- reference CPU op path (exact multiply; timing baseline) ------------

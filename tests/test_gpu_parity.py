@@ -463,3 +463,38 @@ def test_reference_conv_test_matrix(ops, oracle, luts, stride):
                 else:
                     for a, b in zip(got, exact):
                         assert np.array_equal(a, b)   # integer products and sums are exact in fast mode
+
+
+def test_int32_ops(ops, oracle, luts):
+    """T = int32 (the reference registers its conv and dense ops for float and
+    int32): operands go through the multiplier as floats, the int32 accumulator
+    is truncated at every step.  Bit-exact vs the oracle."""
+    lut, m = luts["MBM_7"]
+    rng = np.random.default_rng(77)
+    for (n, h, w, c, kh, kw, k, s, pad) in [(2, 7, 6, 3, 3, 3, 5, 1, "SAME"), (1, 9, 9, 4, 3, 2, 6, 2, "VALID"), (2, 6, 6, 2, 5, 5, 3, 2, "SAME")]:
+        g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+        x = rng.integers(-40, 40, size=(n, h, w, c)).astype(np.int32)
+        x[rng.random(x.shape) < 0.3] = 0
+        wt = rng.integers(-9, 9, size=(kh, kw, c, k)).astype(np.int32)
+        dy = rng.integers(-20, 20, size=(n, g.out_h, g.out_w, k)).astype(np.int32)
+        kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=lut_path("MBM_7"))
+        y = ops.convam(dev(x), dev(wt), **kw_)
+        assert y.dtype == torch.int32
+        assert np.array_equal(y.cpu().numpy(), oracle.conv2d_i32("fwd", g, x, wt, lut, m))
+        assert np.array_equal(ops.convam_filter_grad(wt.shape, dev(x), dev(dy), **kw_).cpu().numpy(),
+                              oracle.conv2d_i32("bwd_filter", g, x, dy, lut, m))
+        assert np.array_equal(ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_).cpu().numpy(),
+                              oracle.conv2d_i32("bwd_input", g, wt, dy, lut, m))
+    xd = rng.integers(-30, 30, size=(6, 17)).astype(np.int32)
+    wd = rng.integers(-30, 30, size=(17, 5)).astype(np.int32)
+    gd = rng.integers(-30, 30, size=(6, 5)).astype(np.int32)
+    p = lut_path("MBM_7")
+    assert np.array_equal(ops.denseam(dev(xd), dev(wd), p).cpu().numpy(), oracle.gemm_i32(xd, wd, lut, m))
+    dxx, dww = ops.denseam_grad(dev(gd), dev(xd), dev(wd), p)
+    assert np.array_equal(dww.cpu().numpy(), oracle.gemm_i32(np.ascontiguousarray(xd.T), gd, lut, m))
+    # dx[b,k] = sum_u AM(w[k,u], g[b,u]) with the weight as first operand
+    assert np.array_equal(dxx.cpu().numpy(), np.ascontiguousarray(oracle.gemm_i32(wd, np.ascontiguousarray(gd.T), lut, m).T))
+    with pytest.raises(TypeError):
+        ops.matmulam(dev(xd), dev(wd), mant_mul_lut=p)
+    with pytest.raises(TypeError):
+        ops.denseam(dev(xd), dev(wd.astype(np.float32)), p)
