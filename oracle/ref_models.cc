@@ -40,6 +40,8 @@
 #error "select a model with -D<MULTIPLIER>"
 #endif
 
+extern "C" float ref_model_mul(float a, float b) { return REF_MODEL(a, b); }
+
 extern "C" void ref_model_mul_array(const uint32_t* at, const uint32_t* bt, uint32_t* out, uint64_t n) {
   for (uint64_t i = 0; i < n; ++i) {
     float a, b;
