@@ -15,12 +15,14 @@ ERR_INVALID, ERR_LUT_NAME, ERR_LUT_IO, ERR_LUT_SIZE, ERR_CUDA, ERR_WORKSPACE, ER
 FAST = 0
 DETERMINISTIC = 1
 INT32 = 2
+ACT_NONE, ACT_RELU = 0, 1
 STATIC_SCRATCH_BYTES = 8 << 20
 
 # every symbol include/amsim.h declares
 EXPORTS = [
     "amsim_last_error", "amsim_version", "amsim_lut_open", "amsim_lut_open_bytes", "amsim_lut_close",
-    "amsim_lut_info", "amsim_mul", "amsim_conv2d_geometry", "amsim_conv2d_fwd", "amsim_conv2d_bwd_input",
+    "amsim_lut_info", "amsim_mul", "amsim_conv2d_geometry", "amsim_conv2d_fwd", "amsim_conv2d_fwd_bias_act",
+    "amsim_dense_fwd_bias_act", "amsim_conv2d_bwd_input",
     "amsim_conv2d_bwd_filter_workspace", "amsim_conv2d_bwd_filter", "amsim_conv2d_bwd_filter_static",
     "amsim_dense_fwd",
     "amsim_dense_bwd_weight_workspace", "amsim_dense_bwd_weight", "amsim_dense_bwd_input", "amsim_matmul",
@@ -52,6 +54,8 @@ def _load() -> C.CDLL:
     L.amsim_conv2d_geometry.argtypes = [ip] * 7 + [C.POINTER(ip)] * 4
     conv_dims = [ip] * 13
     L.amsim_conv2d_fwd.argtypes = [vp, vp, fp, fp, fp] + conv_dims + [u]
+    L.amsim_conv2d_fwd_bias_act.argtypes = [vp, vp, fp, fp, fp, fp] + conv_dims + [ip, u]
+    L.amsim_dense_fwd_bias_act.argtypes = [vp, vp, fp, fp, fp, fp, ip, ip, ip, ip, u]
     L.amsim_conv2d_bwd_input.argtypes = [vp, vp, fp, fp, fp] + conv_dims + [u]
     L.amsim_conv2d_bwd_filter_workspace.argtypes = [ip] * 9 + [u]
     L.amsim_conv2d_bwd_filter_workspace.restype = sz

@@ -460,11 +460,13 @@ int amsim_conv2d_geometry(int in_h, int in_w, int f_h, int f_w, int stride_h, in
   return AMSIM_OK;
 }
 
-int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x, const float* w, float* y, int batch, int in_h,
-                     int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w, int stride_h, int stride_w,
-                     int pad_top, int pad_left, unsigned flags) {
+static int conv2d_fwd_impl(void* stream, const amsim_lut* lut, const float* x, const float* w, const float* bias,
+                           float* y, int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
+                           int out_w, int stride_h, int stride_w, int pad_top, int pad_left, int act, unsigned flags) {
   int rc = check_common(lut, flags, true);
   if (rc) return rc;
+  if (act != AMSIM_ACT_NONE && act != AMSIM_ACT_RELU) return fail(AMSIM_ERR_INVALID, "unknown activation %d", act);
+  if ((bias || act) && (flags & AMSIM_INT32)) return fail(AMSIM_ERR_UNSUPPORTED, "the fused epilogue is FP32 only");
   rc = check_conv_dims(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h, stride_w, pad_top, pad_left);
   if (rc) return rc;
   if (batch == 0 || out_h == 0 || out_w == 0) return AMSIM_OK;
@@ -479,8 +481,25 @@ int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x, const f
   p.u_t0 = 0; p.u_tj = f_w; p.u_ti = 1; p.u_tap = (long long)in_c * out_c; p.u_sk = out_c; p.u_sq = 1;
   p.o_sp = out_c; p.o_sq = 1;
   fill_lut(p, lut, /*v_is_first_operand=*/true);
+  p.bias = bias;
+  p.relu = act == AMSIM_ACT_RELU;
   if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, false);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
+}
+
+int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x, const float* w, float* y, int batch, int in_h,
+                     int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w, int stride_h, int stride_w,
+                     int pad_top, int pad_left, unsigned flags) {
+  return conv2d_fwd_impl(stream, lut, x, w, nullptr, y, batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h,
+                         stride_w, pad_top, pad_left, AMSIM_ACT_NONE, flags);
+}
+
+int amsim_conv2d_fwd_bias_act(void* stream, const amsim_lut* lut, const float* x, const float* w, const float* bias,
+                              float* y, int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
+                              int out_w, int stride_h, int stride_w, int pad_top, int pad_left, int act,
+                              unsigned flags) {
+  return conv2d_fwd_impl(stream, lut, x, w, bias, y, batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h,
+                         stride_w, pad_top, pad_left, act, flags);
 }
 
 int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, const float* dy, float* dx, int batch,
@@ -640,10 +659,12 @@ static int check_dense(int batch, int units, int input_width) {
   return AMSIM_OK;
 }
 
-int amsim_dense_fwd(void* stream, const amsim_lut* lut, const float* x, const float* w, float* y, int batch, int units,
-                    int input_width, unsigned flags) {
+static int dense_fwd_impl(void* stream, const amsim_lut* lut, const float* x, const float* w, const float* bias,
+                          float* y, int batch, int units, int input_width, int act, unsigned flags) {
   int rc = check_common(lut, flags, true);
   if (rc) return rc;
+  if (act != AMSIM_ACT_NONE && act != AMSIM_ACT_RELU) return fail(AMSIM_ERR_INVALID, "unknown activation %d", act);
+  if ((bias || act) && (flags & AMSIM_INT32)) return fail(AMSIM_ERR_UNSUPPORTED, "the fused epilogue is FP32 only");
   if ((rc = check_dense(batch, units, input_width))) return rc;
   if (batch == 0) return AMSIM_OK;
   if (!x || !w || !y) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
@@ -654,8 +675,20 @@ int amsim_dense_fwd(void* stream, const amsim_lut* lut, const float* x, const fl
   p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = units; p.u_sq = 1;
   p.o_sp = units; p.o_sq = 1;
   fill_lut(p, lut, true);
+  p.bias = bias;
+  p.relu = act == AMSIM_ACT_RELU;
   if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, false);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
+}
+
+int amsim_dense_fwd(void* stream, const amsim_lut* lut, const float* x, const float* w, float* y, int batch, int units,
+                    int input_width, unsigned flags) {
+  return dense_fwd_impl(stream, lut, x, w, nullptr, y, batch, units, input_width, AMSIM_ACT_NONE, flags);
+}
+
+int amsim_dense_fwd_bias_act(void* stream, const amsim_lut* lut, const float* x, const float* w, const float* bias,
+                             float* y, int batch, int units, int input_width, int act, unsigned flags) {
+  return dense_fwd_impl(stream, lut, x, w, bias, y, batch, units, input_width, act, flags);
 }
 
 int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w, const float* g_, float* dx, int batch,

@@ -130,6 +130,9 @@ struct Params {
   int ksplit;
   int tile_bytes;               // bytes reserved before the table (operand tiles, or the exchange buffer)
   int v_first;                  // the lane operand V is the multiplier's first operand (int32 kernels)
+  // gather_gemm epilogue: out = act(acc + bias[q]); both optional (exact FP32 add, then max with 0)
+  const float* bias;
+  int relu;
   // fgrad only
   int k_chunk, splits;
   float* ws;                    // [splits][P][Q] partial sums when splits > 1
@@ -460,13 +463,20 @@ AMSIM_UNROLL_K
 #pragma unroll
     for (int g4 = 0; g4 < TR / 4; ++g4) {
       const int qg = q0 + ucol + 4 * g4;
+      float o[4] = {acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]};
+      if (prm.bias != nullptr || prm.relu) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          if (prm.bias != nullptr && qg + r < prm.Q) o[r] = __fadd_rn(o[r], __ldg(prm.bias + qg + r));
+          if (prm.relu) o[r] = o[r] < 0.f ? 0.f : o[r];
+        }
+      }
       if (vec_out && qg + 3 < prm.Q) {
-        *reinterpret_cast<float4*>(orow + qg) =
-            make_float4(acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]);
+        *reinterpret_cast<float4*>(orow + qg) = make_float4(o[0], o[1], o[2], o[3]);
       } else {
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-          if (qg + r < prm.Q) orow[(long long)(qg + r) * prm.o_sq] = acc[4 * g4 + r][c];
+          if (qg + r < prm.Q) orow[(long long)(qg + r) * prm.o_sq] = o[r];
       }
     }
   }

@@ -63,6 +63,53 @@ class _DenseamFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
+class _ConvamBiasActFn(torch.autograd.Function):
+    """act(Convam(x, w) + b) with the bias add and ReLU fused into the forward
+    kernel; backward masks the gradient with the saved output (ReLU), reduces the
+    bias gradient and then follows the Convam gradient wiring."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, strides, padding, activation, lut, deterministic):
+        y = ops.convam_bias_act(x, w, b, strides=strides, padding=padding, activation=activation, mant_mul_lut=lut,
+                                deterministic=deterministic)
+        ctx.save_for_backward(x, w, y if activation == "relu" else None)
+        ctx.cfg = (strides, padding, lut, deterministic, b is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, y = ctx.saved_tensors
+        strides, padding, lut, det, has_bias = ctx.cfg
+        g = dy * (y > 0) if y is not None else dy
+        g = g.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = ops.convam_input_grad(x.shape, w, g, strides=strides, padding=padding, mant_mul_lut=lut, deterministic=det)
+        if ctx.needs_input_grad[1]:
+            dw = ops.convam_filter_grad(w.shape, x, g, strides=strides, padding=padding, mant_mul_lut=lut, deterministic=det)
+        if has_bias and ctx.needs_input_grad[2]:
+            db = g.sum((0, 1, 2))
+        return dx, dw, db, None, None, None, None, None
+
+
+class _DenseamBiasActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, activation, lut, deterministic):
+        y = ops.denseam_bias_act(x, w, b, activation=activation, mant_mul_lut=lut, deterministic=deterministic)
+        ctx.save_for_backward(x, w, y if activation == "relu" else None)
+        ctx.cfg = (lut, deterministic, b is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, y = ctx.saved_tensors
+        lut, det, has_bias = ctx.cfg
+        g = (dy * (y > 0) if y is not None else dy).contiguous()
+        dx, dw = ops.denseam_grad(g, x, w, lut, deterministic=det)
+        db = g.sum(0) if has_bias and ctx.needs_input_grad[2] else None
+        return dx, dw, db, None, None, None
+
+
 class _MatMulAMFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, a, b, lut, deterministic):
@@ -140,8 +187,11 @@ class AMConv2D(nn.Module):
                 self.kernel.uniform_(-lim, lim)
 
     def forward(self, x):
-        y = amconv2d(x, self.kernel, [1, self.strides[0], self.strides[1], 1], self.padding, self.mant_mul_lut,
-                     self.deterministic)
+        st = [1, self.strides[0], self.strides[1], 1]
+        if self.activation in (None, "linear", "relu") and (self.bias is not None or self.activation == "relu"):
+            return _ConvamBiasActFn.apply(x, self.kernel, self.bias, st, self.padding, self.activation,
+                                          self.mant_mul_lut, self.deterministic)
+        y = amconv2d(x, self.kernel, st, self.padding, self.mant_mul_lut, self.deterministic)
         if self.bias is not None:
             y = y + self.bias
         return _ACT[self.activation](y)
@@ -167,6 +217,11 @@ class denseam(nn.Module):
                 self.kernel.uniform_(-lim, lim)
 
     def forward(self, x):
+        if self.activation in (None, "linear", "relu") and (self.bias is not None or self.activation == "relu"):
+            lead = x.shape[:-1]
+            y = _DenseamBiasActFn.apply(x.reshape(-1, x.shape[-1]).contiguous(), self.kernel, self.bias,
+                                        self.activation, self.mant_mul_lut, self.deterministic)
+            return y.reshape(*lead, self.kernel.shape[1])
         y = amdense(x, self.kernel, self.mant_mul_lut, self.deterministic)
         if self.bias is not None:
             y = y + self.bias

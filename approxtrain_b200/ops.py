@@ -32,7 +32,7 @@ from ._lib import AmsimError, lib, check
 
 __all__ = [
     "AMLut", "get_lut", "am_multiply", "conv2d_geometry", "convam", "convam_input_grad", "convam_filter_grad",
-    "denseam", "denseam_grad", "matmulam", "AmsimError",
+    "denseam", "denseam_grad", "matmulam", "convam_bias_act", "denseam_bias_act", "AmsimError",
 ]
 
 
@@ -194,6 +194,66 @@ def convam(input: torch.Tensor, filter: torch.Tensor, strides=None, padding="VAL
     with torch.cuda.device(x.device):
         check(lib.amsim_conv2d_fwd(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(y), n, h, wd, c, kh, kw, k, oh, ow,
                                    sh, sw, pt, pl, _flags(deterministic) | _dtype_flag(x, w)))
+    return y
+
+
+def _act_code(activation) -> int:
+    if activation in (None, "linear"):
+        return _lib.ACT_NONE
+    if activation == "relu":
+        return _lib.ACT_RELU
+    raise ValueError(f"only None / 'relu' can be fused into the op, got {activation!r}")
+
+
+def convam_bias_act(input: torch.Tensor, filter: torch.Tensor, bias, strides=None, padding="VALID",
+                    activation=None, mant_mul_lut: str = "", deterministic: bool = False) -> torch.Tensor:
+    """``act(convam(input, filter) + bias)`` in one launch: the exact bias add and
+    ReLU that follow the op in the reference's Keras layer
+    (am_convolutional.py:267-292) run in the kernel's epilogue, bit-identical to
+    the unfused sequence.  ``bias`` may be None."""
+    x, w = _prep(input, "input"), _prep(filter, "filter")
+    if x.dtype != torch.float32 or w.dtype != torch.float32:
+        raise TypeError("the fused epilogue is float32 only")
+    n, h, wd, c = x.shape
+    kh, kw, ci, k = w.shape
+    if c != ci:
+        raise ValueError(f"input depth must be evenly divisible by filter depth: {c} vs {ci}")
+    b = None
+    if bias is not None:
+        b = _prep(bias, "bias")
+        if b.dtype != torch.float32 or tuple(b.shape) != (k,):
+            raise ValueError("bias must be float32 of shape [filters]")
+    sh, sw = _hw(strides, "strides")
+    oh, ow, pt, pl = conv2d_geometry(h, wd, kh, kw, sh, sw, padding)
+    lut = get_lut(mant_mul_lut, x.device)
+    y = torch.empty((n, oh, ow, k), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.amsim_conv2d_fwd_bias_act(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(b) if b is not None else None,
+                                            _ptr(y), n, h, wd, c, kh, kw, k, oh, ow, sh, sw, pt, pl,
+                                            _act_code(activation), _flags(deterministic)))
+    return y
+
+
+def denseam_bias_act(input: torch.Tensor, weights: torch.Tensor, bias, activation=None, mant_mul_lut: str = "",
+                     deterministic: bool = False) -> torch.Tensor:
+    """``act(denseam(input, weights) + bias)`` in one launch (amdenselayer.py:222-226 fused)."""
+    x, w = _prep(input, "input"), _prep(weights, "weights")
+    if x.dtype != torch.float32 or w.dtype != torch.float32:
+        raise TypeError("the fused epilogue is float32 only")
+    if x.dim() != 2 or w.dim() != 2 or w.shape[0] != x.shape[1]:
+        raise ValueError("Denseam takes input [batch, width] and weights [width, units]")
+    bsz, kin = x.shape
+    u = w.shape[1]
+    b = None
+    if bias is not None:
+        b = _prep(bias, "bias")
+        if b.dtype != torch.float32 or tuple(b.shape) != (u,):
+            raise ValueError("bias must be float32 of shape [units]")
+    lut = get_lut(mant_mul_lut, x.device)
+    y = torch.empty((bsz, u), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.amsim_dense_fwd_bias_act(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(b) if b is not None else None,
+                                           _ptr(y), bsz, u, kin, _act_code(activation), _flags(deterministic)))
     return y
 
 

@@ -117,6 +117,24 @@ int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x,
                      int stride_h, int stride_w, int pad_top, int pad_left,
                      unsigned flags);
 
+/* Forward with the layer's exact epilogue fused in: y = act(conv(x, w) + bias).
+ * In the reference the bias add and the activation are separate TensorFlow ops
+ * after Convam / Denseam (python/keras/layers/am_convolutional.py:267-292,
+ * amdenselayer.py:222-226); here they run in the kernel's epilogue with the
+ * same arithmetic (one FP32 add per output, then max with 0), so the result
+ * equals the unfused sequence bit for bit.  `bias` (out_c floats) may be NULL;
+ * `act`: 0 = none, 1 = ReLU.  FP32 only. */
+#define AMSIM_ACT_NONE 0
+#define AMSIM_ACT_RELU 1
+int amsim_conv2d_fwd_bias_act(void* stream, const amsim_lut* lut, const float* x,
+                              const float* w, const float* bias, float* y, int batch,
+                              int in_h, int in_w, int in_c, int f_h, int f_w, int out_c,
+                              int out_h, int out_w, int stride_h, int stride_w,
+                              int pad_top, int pad_left, int act, unsigned flags);
+int amsim_dense_fwd_bias_act(void* stream, const amsim_lut* lut, const float* x,
+                             const float* w, const float* bias, float* y, int batch,
+                             int units, int input_width, int act, unsigned flags);
+
 /* Input gradient: replaces ConvamInputGradFunctor<GPUDevice> (convam.h:82-93,
  * cuda/cuda_kernel.cu:462-657) including cuda/reverseNswapdim23.cu.  The
  * functor's hole_grad_* and back-pad arguments are derived here from the

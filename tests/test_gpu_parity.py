@@ -498,3 +498,38 @@ def test_int32_ops(ops, oracle, luts):
         ops.matmulam(dev(xd), dev(wd), mant_mul_lut=p)
     with pytest.raises(TypeError):
         ops.denseam(dev(xd), dev(wd.astype(np.float32)), p)
+
+
+def test_fused_bias_relu_epilogue_equals_unfused_sequence(ops, oracle, luts):
+    """act(op(x, w) + bias) in the kernel epilogue vs op, then FP32 add, then
+    ReLU as separate exact steps: bit-identical, both modes, including a shape
+    that takes the cluster-split path."""
+    lut, m = luts["MBM_7"]
+    p = lut_path("MBM_7")
+    rng = np.random.default_rng(55)
+    for (n, h, w, c, kh, kw, k, s, pad) in [(2, 9, 9, 8, 3, 3, 20, 1, "SAME"), (2, 7, 7, 64, 3, 3, 96, 1, "SAME"), (1, 8, 8, 3, 5, 5, 6, 2, "VALID")]:
+        x, wt = _conv_case(rng, n, h, w, c, kh, kw, k)
+        b = rng.standard_normal(k).astype(np.float32)
+        g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+        for det in (True, False):
+            kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=p, deterministic=det)
+            base = ops.convam(dev(x), dev(wt), **kw_)
+            for act in (None, "relu"):
+                want = base + dev(b)
+                if act == "relu":
+                    want = torch.relu(want)
+                got = ops.convam_bias_act(dev(x), dev(wt), dev(b), activation=act, **kw_)
+                assert torch.equal(got, want), (det, act)
+            assert torch.equal(ops.convam_bias_act(dev(x), dev(wt), None, activation="relu", **kw_), torch.relu(base))
+        ref = np.maximum(oracle.conv2d_fwd(g, x, wt, lut, m) + b, 0).astype(np.float32)
+        got = ops.convam_bias_act(dev(x), dev(wt), dev(b), strides=[1, s, s, 1], padding=pad, activation="relu",
+                                  mant_mul_lut=p, deterministic=True).cpu().numpy()
+        assert np.array_equal(got, ref)
+    xd = rng.standard_normal((33, 50)).astype(np.float32)
+    wd = rng.standard_normal((50, 70)).astype(np.float32)
+    bd = rng.standard_normal(70).astype(np.float32)
+    for det in (True, False):
+        want = torch.relu(ops.denseam(dev(xd), dev(wd), p, deterministic=det) + dev(bd))
+        assert torch.equal(ops.denseam_bias_act(dev(xd), dev(wd), dev(bd), activation="relu", mant_mul_lut=p, deterministic=det), want)
+    with pytest.raises(ValueError):
+        ops.denseam_bias_act(dev(xd), dev(wd), dev(bd), activation="tanh", mant_mul_lut=p)
