@@ -533,3 +533,51 @@ def test_fused_bias_relu_epilogue_equals_unfused_sequence(ops, oracle, luts):
         assert torch.equal(ops.denseam_bias_act(dev(xd), dev(wd), dev(bd), activation="relu", mant_mul_lut=p, deterministic=det), want)
     with pytest.raises(ValueError):
         ops.denseam_bias_act(dev(xd), dev(wd), dev(bd), activation="tanh", mant_mul_lut=p)
+
+
+def test_lut_handle_cache_and_lifecycle(ops):
+    """Handles are shared per (real path, device) and reference counted
+    (the reference keeps one private copy per OpKernel: convam.cc:498-499,712,979)."""
+    import ctypes as C
+    from approxtrain_b200 import _lib
+    p = lut_path("MIT_3").encode()
+    h1, h2 = C.c_void_p(), C.c_void_p()
+    assert _lib.lib.amsim_lut_open(p, 0, C.byref(h1)) == 0
+    rel = os.path.relpath(lut_path("MIT_3")).encode()          # another spelling of the same file
+    assert _lib.lib.amsim_lut_open(rel, 0, C.byref(h2)) == 0
+    assert h1.value == h2.value
+    m, mask, a_s, b_s, ptr = C.c_int(), C.c_uint32(), C.c_int(), C.c_int(), C.c_void_p()
+    assert _lib.lib.amsim_lut_info(h1, C.byref(m), C.byref(mask), C.byref(a_s), C.byref(b_s), C.byref(ptr)) == 0
+    assert (m.value, mask.value, a_s.value, b_s.value) == (3, 0x700000, 17, 20)   # approx_mul_lut.h:26-28
+    assert _lib.lib.amsim_lut_close(h1) == 0
+    # still usable through the second reference
+    x = torch.randn(4, 8, device="cuda")
+    w = torch.randn(8, 4, device="cuda")
+    y = torch.empty(4, 4, device="cuda")
+    assert _lib.lib.amsim_dense_fwd(None, h2, C.c_void_p(x.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(y.data_ptr()), 4, 4, 8, 0) == 0
+    torch.cuda.synchronize()
+    assert _lib.lib.amsim_lut_close(h2) == 0
+    assert _lib.lib.amsim_lut_close(None) == 0
+
+
+def test_concurrent_streams_do_not_interfere(ops, oracle, luts):
+    """Calls are stream-ordered and re-entrant: two streams running split-K filter
+    gradients (each with its own workspace) and forward passes at the same time
+    give the results of running them one after the other."""
+    p = lut_path("MBM_7")
+    g = torch.Generator(device="cuda").manual_seed(9)
+    xs = [torch.randn(8, 20, 20, 16, device="cuda", generator=g) for _ in range(2)]
+    ws = [torch.randn(3, 3, 16, 32, device="cuda", generator=g) for _ in range(2)]
+    dys = [torch.randn(8, 20, 20, 32, device="cuda", generator=g) for _ in range(2)]
+    kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=p)
+    want = [(ops.convam(x, w, **kw_), ops.convam_filter_grad(w.shape, x, dy, **kw_)) for x, w, dy in zip(xs, ws, dys)]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    got = [None, None]
+    for rep in range(5):
+        for i, s in enumerate(streams):
+            with torch.cuda.stream(s):
+                got[i] = (ops.convam(xs[i], ws[i], **kw_), ops.convam_filter_grad(ws[i].shape, xs[i], dys[i], **kw_))
+        torch.cuda.synchronize()
+        for i in range(2):
+            assert torch.equal(got[i][0], want[i][0]) and torch.equal(got[i][1], want[i][1])
