@@ -7,10 +7,11 @@
 #   oracle/_ref/lut/MBM_11.bin     m = 11 LUT from cuda/FPmultMBM_fast32.inl
 #   oracle/_ref/libref_model_<LUT>.so   the functional model each shipped LUT was generated from
 # Reference sources are compiled where they lie; nothing is copied.
-# Usage: oracle/build.sh [reference_dir]   (default /root/reference)
+# Usage: oracle/build.sh [reference_dir]
+# (default: $AMSIM_REFERENCE_DIR, else the directory "reference" beside this repository)
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-ref="${1:-${AMSIM_REFERENCE_DIR:-/root/reference}}"
+ref="${1:-${AMSIM_REFERENCE_DIR:-$here/../../reference}}"
 
 gcc -O2 -fPIC -shared -fopenmp -ffp-contract=off -fno-fast-math -std=c11 \
     -o "$here/libamsim_oracle.so" "$here/amsim_oracle.c" -lm

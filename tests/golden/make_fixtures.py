@@ -1,5 +1,5 @@
 """Regenerates the committed golden fixtures.  Needs a reference checkout
-(default /root/reference); run from the repository root:
+(default: the directory "reference" beside this repository); run from the repository root:
 
     python tests/golden/make_fixtures.py [reference_dir]
 
@@ -50,7 +50,7 @@ def prim_operands(seed: int):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(ROOT), "reference")
     subprocess.check_call(["bash", os.path.join(ROOT, "oracle", "build.sh"), ref])
     from oracle.oracle import Oracle, RefPrimitive, load_lut
 
