@@ -581,3 +581,29 @@ def test_concurrent_streams_do_not_interfere(ops, oracle, luts):
         torch.cuda.synchronize()
         for i in range(2):
             assert torch.equal(got[i][0], want[i][0]) and torch.equal(got[i][1], want[i][1])
+
+
+def test_oversize_and_invalid_arguments_are_refused_before_any_launch(ops):
+    """Index arithmetic is 32-bit for rows and the reduction: shapes beyond it are
+    refused with a status, nothing is launched (the reference would overflow its
+    int products silently)."""
+    import ctypes as C
+    from approxtrain_b200 import _lib
+    lut = ops.get_lut(lut_path("MBM_7"), "cuda")
+    t = torch.zeros(16, device="cuda")
+    P = C.c_void_p(t.data_ptr())
+    L = _lib.lib
+    # 2^20 images of 64x64: more than 2^31 pixels
+    assert L.amsim_conv2d_fwd(None, lut.handle, P, P, P, 1 << 20, 64, 64, 4, 3, 3, 4, 64, 64, 1, 1, 1, 1, 0) == _lib.ERR_UNSUPPORTED
+    # reduction length beyond 2^30
+    assert L.amsim_conv2d_fwd(None, lut.handle, P, P, P, 1, 4096, 4096, 1 << 16, 128, 128, 4, 3969, 3969, 1, 1, 0, 0, 0) == _lib.ERR_UNSUPPORTED
+    # non-positive stride, negative padding, unknown flag bits, NULL tensors
+    assert L.amsim_conv2d_fwd(None, lut.handle, P, P, P, 1, 4, 4, 1, 3, 3, 1, 2, 2, 0, 1, 0, 0, 0) == _lib.ERR_INVALID
+    assert L.amsim_conv2d_fwd(None, lut.handle, P, P, P, 1, 4, 4, 1, 3, 3, 1, 2, 2, 1, 1, -1, 0, 0) == _lib.ERR_INVALID
+    assert L.amsim_conv2d_fwd(None, lut.handle, P, P, P, 1, 4, 4, 1, 3, 3, 1, 2, 2, 1, 1, 0, 0, 64) == _lib.ERR_INVALID
+    assert L.amsim_conv2d_fwd(None, lut.handle, None, P, P, 1, 4, 4, 1, 3, 3, 1, 2, 2, 1, 1, 0, 0, 0) == _lib.ERR_INVALID
+    assert L.amsim_dense_fwd(None, None, P, P, P, 2, 2, 2, 0) == _lib.ERR_INVALID
+    assert L.amsim_matmul(None, lut.handle, P, P, P, 0, 0, 2, 3, 4, 2, 0) == _lib.ERR_INVALID
+    assert b"cols of mat a" in L.amsim_last_error()
+    assert L.amsim_conv2d_fwd_bias_act(None, lut.handle, P, P, None, P, 1, 4, 4, 1, 3, 3, 1, 2, 2, 1, 1, 0, 0, 7, 0) == _lib.ERR_INVALID
+    torch.cuda.synchronize()
