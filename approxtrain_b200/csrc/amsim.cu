@@ -53,6 +53,7 @@ struct amsim_lut {
   uint8_t* d_canon = nullptr;  // encoded, row = first operand (a)   [m <= 7]
   uint8_t* d_trans = nullptr;  // encoded, row = second operand (b)  [m <= 7]
   int enc_bytes = 0;           // size of each encoded copy, multiple of 16
+  bool additive = false;       // encoded entry(i, j) == i + j for every pair: no lookups needed
 };
 
 namespace {
@@ -102,12 +103,17 @@ int upload_lut(const uint8_t* bytes, int m, int device, amsim_lut** out) {
     const int side = 1 << m, stride = side;
     h->enc_bytes = (side * stride + 15) / 16 * 16;
     std::vector<uint8_t> canon(h->enc_bytes, 0), trans(h->enc_bytes, 0);
+    bool additive = true;
     for (int a = 0; a < side; ++a)
       for (int b = 0; b < side; ++b) {
         const uint8_t v = encode_entry(bytes[a * side + b], m);
         canon[a * stride + b] = v;
         trans[b * stride + a] = v;
+        additive = additive && (int)v == a + b;
       }
+    // Mitchell-type tables: (carry << m) + mantissa == i + j everywhere, i.e. the multiplier adds the
+    // operands' truncated mantissa fields.  The kernels then skip the table (bit-identical result).
+    h->additive = additive && !getenv("AMSIM_NO_ADDITIVE");
     e = cudaMalloc(&h->d_canon, h->enc_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&h->d_trans, h->enc_bytes);
     if (e == cudaSuccess) e = cudaMemcpy(h->d_canon, canon.data(), h->enc_bytes, cudaMemcpyHostToDevice);
@@ -171,6 +177,7 @@ void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
   p.rmask = ((1u << lut->m) - 1u) << lut->m;
   p.cmask = (1u << lut->m) - 1u;
   p.cadj = (1u << 23) - 128u * p.mult;
+  p.lut_mode = lut->m > 7 ? LM_GLOBAL : (lut->additive ? LM_ADD : LM_SMEM);
   p.lut_raw = v_is_first_operand ? lut->d_raw_t : lut->d_raw;
   p.v_first = v_is_first_operand ? 1 : 0;
   uint32_t al = 16;
@@ -189,14 +196,14 @@ void fill_gather_divs(Gather& g) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-template <bool EXACT, bool VEC, bool GLUT>
+template <bool EXACT, bool VEC, int LM>
 int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   using L = SmemLayout<1>;
   const int ptiles = (p.P + L::BP - 1) / L::BP, qtiles = (p.Q + BQ - 1) / BQ;
   // Fast mode: when the tiles alone cannot fill the resident CTA slots, a
   // thread-block cluster of `ksplit` CTAs shares each tile's reduction.
   int ksplit = 1;
-  if (!EXACT && !GLUT) {
+  if (!EXACT && LM != LM_GLOBAL) {
     const long long ctas = (long long)ptiles * qtiles * batch;
     const int slots = 148 * AMSIM_CTAS1;
     const int nkb = (p.K + BK - 1) / BK;
@@ -206,16 +213,16 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   p.ksplit = ksplit;
   p.tile_bytes = L::TILE_BYTES;
   if (ksplit > 1 && L::EXCHANGE_BYTES > p.tile_bytes) p.tile_bytes = L::EXCHANGE_BYTES;
-  const size_t smem = GLUT ? (size_t)p.tile_bytes + 16 : L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
+  const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
   if (ksplit == 1) {
-    int rc = ensure_smem(gather_gemm<1, EXACT, VEC, false, GLUT>, smem, device);
+    int rc = ensure_smem(gather_gemm<1, EXACT, VEC, false, LM>, smem, device);
     if (rc) return rc;
-    gather_gemm<1, EXACT, VEC, false, GLUT><<<dim3(ptiles, qtiles, batch), L::NT, smem, st>>>(p);
+    gather_gemm<1, EXACT, VEC, false, LM><<<dim3(ptiles, qtiles, batch), L::NT, smem, st>>>(p);
     CUDA_TRY(cudaGetLastError());
     return AMSIM_OK;
   }
-  constexpr bool kCanCluster = !EXACT && !GLUT;
-  int rc = ensure_smem(gather_gemm<1, EXACT, VEC, kCanCluster, GLUT>, smem, device);
+  constexpr bool kCanCluster = !EXACT && LM != LM_GLOBAL;
+  int rc = ensure_smem(gather_gemm<1, EXACT, VEC, kCanCluster, LM>, smem, device);
   if (rc) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -230,7 +237,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, gather_gemm<1, EXACT, VEC, kCanCluster, GLUT>, p));
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, gather_gemm<1, EXACT, VEC, kCanCluster, LM>, p));
   return AMSIM_OK;
 }
 
@@ -238,15 +245,16 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
   if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
   if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
-  const bool glut = p.m > 7;  // table too large for shared memory: global / L2 lookups
-#define AMSIM_GO(EX_, VEC_, GL_) return launch_gather_t<EX_, VEC_, GL_>(st, p, batch, device)
-  if (glut) {
-    if (exact) { if (vec) AMSIM_GO(true, true, true); else AMSIM_GO(true, false, true); }
-    else       { if (vec) AMSIM_GO(false, true, true); else AMSIM_GO(false, false, true); }
-  } else {
-    if (exact) { if (vec) AMSIM_GO(true, true, false); else AMSIM_GO(true, false, false); }
-    else       { if (vec) AMSIM_GO(false, true, false); else AMSIM_GO(false, false, false); }
-  }
+#define AMSIM_GO(EX_, VEC_, LM_) return launch_gather_t<EX_, VEC_, LM_>(st, p, batch, device)
+#define AMSIM_GO_LM(LM_)                                                                        \
+  do {                                                                                          \
+    if (exact) { if (vec) AMSIM_GO(true, true, LM_); else AMSIM_GO(true, false, LM_); }         \
+    else       { if (vec) AMSIM_GO(false, true, LM_); else AMSIM_GO(false, false, LM_); }       \
+  } while (0)
+  if (p.lut_mode == LM_ADD) AMSIM_GO_LM(LM_ADD);
+  if (p.lut_mode == LM_GLOBAL) AMSIM_GO_LM(LM_GLOBAL);
+  AMSIM_GO_LM(LM_SMEM);
+#undef AMSIM_GO_LM
 #undef AMSIM_GO
 }
 
@@ -278,14 +286,14 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
   return f;
 }
 
-template <bool EXACT, bool VEC, bool GLUT>
+template <bool EXACT, bool VEC, int LM>
 int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   using L = SmemLayout<1>;
-  const size_t smem = GLUT ? (size_t)L::TILE_BYTES + 16 : L::bytes(L::TILE_BYTES, p.lut_bytes, p.lut_align);
-  int rc = ensure_smem(fgrad_gemm<1, EXACT, VEC, GLUT>, smem, device);
+  const size_t smem = LM != LM_SMEM ? (size_t)L::TILE_BYTES + 16 : L::bytes(L::TILE_BYTES, p.lut_bytes, p.lut_align);
+  int rc = ensure_smem(fgrad_gemm<1, EXACT, VEC, LM>, smem, device);
   if (rc) return rc;
   dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, p.splits);
-  fgrad_gemm<1, EXACT, VEC, GLUT><<<grid, L::NT, smem, st>>>(p);
+  fgrad_gemm<1, EXACT, VEC, LM><<<grid, L::NT, smem, st>>>(p);
   CUDA_TRY(cudaGetLastError());
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
@@ -307,15 +315,16 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   p.k_chunk = f.k_chunk;
   p.ws = static_cast<float*>(ws);
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
-  const bool glut = p.m > 7;
-#define AMSIM_GO(EX_, VEC_, GL_) return launch_fgrad_t<EX_, VEC_, GL_>(st, p, device)
-  if (glut) {
-    if (exact) { if (vec) AMSIM_GO(true, true, true); else AMSIM_GO(true, false, true); }
-    else       { if (vec) AMSIM_GO(false, true, true); else AMSIM_GO(false, false, true); }
-  } else {
-    if (exact) { if (vec) AMSIM_GO(true, true, false); else AMSIM_GO(true, false, false); }
-    else       { if (vec) AMSIM_GO(false, true, false); else AMSIM_GO(false, false, false); }
-  }
+#define AMSIM_GO(EX_, VEC_, LM_) return launch_fgrad_t<EX_, VEC_, LM_>(st, p, device)
+#define AMSIM_GO_LM(LM_)                                                                        \
+  do {                                                                                          \
+    if (exact) { if (vec) AMSIM_GO(true, true, LM_); else AMSIM_GO(true, false, LM_); }         \
+    else       { if (vec) AMSIM_GO(false, true, LM_); else AMSIM_GO(false, false, LM_); }       \
+  } while (0)
+  if (p.lut_mode == LM_ADD) AMSIM_GO_LM(LM_ADD);
+  if (p.lut_mode == LM_GLOBAL) AMSIM_GO_LM(LM_GLOBAL);
+  AMSIM_GO_LM(LM_SMEM);
+#undef AMSIM_GO_LM
 #undef AMSIM_GO
 }
 

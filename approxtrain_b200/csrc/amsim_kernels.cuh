@@ -129,6 +129,7 @@ struct Params {
   // combine their register tiles through distributed shared memory (1 = no split)
   int ksplit;
   int tile_bytes;               // bytes reserved before the table (operand tiles, or the exchange buffer)
+  int lut_mode;                 // LM_SMEM / LM_GLOBAL / LM_ADD (host-side dispatch)
   int v_first;                  // the lane operand V is the multiplier's first operand (int32 kernels)
   // gather_gemm epilogue: out = act(acc + bias[q]); both optional (exact FP32 add, then max with 0)
   const float* bias;
@@ -148,16 +149,30 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// Where the products' table bits come from.
+constexpr int LM_SMEM = 0;    // 2^m x 2^m byte table in shared memory (m <= 7)
+constexpr int LM_GLOBAL = 1;  // raw table in global memory, L2-resident (m = 8..11)
+constexpr int LM_ADD = 2;     // additive table, entry(i, j) == i + j for every pair (Mitchell-type
+                              // multipliers): the lookup is an integer add of the operands' mantissa
+                              // fields, no table access at all; detected when the LUT is opened
+
 // ---- operand encodings -------------------------------------------------------
 // Lane operand (V): one word = sign+exponent bits | table column.
 //   fast:  a zero exponent field (zero or denormal) becomes the word 0, which
 //          the inner loop predicates off: the product is exactly 0.
 //   exact: the raw fields, nothing special-cased (the reference pushes zeros
 //          and denormals through the table like any other value).
-template <bool EXACT>
+//   additive table: the word keeps the top-m mantissa bits in place instead of
+//          a column index (sign | exponent | truncated mantissa).
+template <bool EXACT, int LM>
 __device__ __forceinline__ uint32_t enc_v(uint32_t bits, int m) {
-  const uint32_t idx = (bits >> (23 - m)) & ((1u << m) - 1u);
-  const uint32_t w = (bits & 0xFF800000u) | idx;
+  uint32_t w;
+  if (LM == LM_ADD) {
+    w = bits & ~((1u << (23 - m)) - 1u);
+  } else {
+    const uint32_t idx = (bits >> (23 - m)) & ((1u << m) - 1u);
+    w = (bits & 0xFF800000u) | idx;
+  }
   if (EXACT) return w;
   return (bits & 0x7F800000u) ? w : 0u;
 }
@@ -166,9 +181,9 @@ __device__ __forceinline__ uint32_t enc_v(uint32_t bits, int m) {
 //   vrow : 4 consecutive lane-operand words (sign+exponent | column)
 //   urow : 16 uniform-operand words (sign+exponent | column << m)
 //   lut_base : shared-memory address of the table (aligned to its size)
-//   GLUT : the table stays in global memory (L2-resident, m = 8..11) as raw bytes;
-//          lut_base is then unused and `lut_g` points at the table.
-template <bool EXACT, bool GLUT>
+//   LM   : LM_SMEM table in shared memory at lut_base; LM_GLOBAL raw table in global
+//          memory at lut_g; LM_ADD no table (additive: an integer add of mantissa fields).
+template <bool EXACT, int LM>
 __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* __restrict__ vrow,
                                          const uint32_t* __restrict__ urow, const uint32_t lut_base,
                                          const uint32_t rmask, const uint32_t mult, const uint32_t cmask,
@@ -180,14 +195,15 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
   bool nz[TC];
 #pragma unroll
   for (int t = 0; t < TC; ++t) {
-    ci[t] = GLUT ? (w[t] & cmask) : ((w[t] & 0xFFu) | lut_base);
+    ci[t] = LM == LM_GLOBAL ? (w[t] & cmask) : ((w[t] & 0xFFu) | lut_base);
     nz[t] = w[t] != 0u;
     if (EXACT) {
       // AMsimulator.inl:26-33: exponent sum - 127, folded into the lane word
-      cs[t] = (w[t] & 0xFF800000u) - 0x3F800000u;
+      // (additive table: the word's mantissa field stays in, it IS the table term)
+      cs[t] = (LM == LM_ADD ? w[t] : (w[t] & 0xFF800000u)) - 0x3F800000u;
       cn[t] = (int)(0x3F800000u - (w[t] & 0x7F800000u));
     } else {
-      cs[t] = w[t] & 0xFF800000u;
+      cs[t] = LM == LM_ADD ? w[t] : (w[t] & 0xFF800000u);
     }
   }
 #pragma unroll
@@ -198,11 +214,14 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
     for (int r = 0; r < 4; ++r) {
       const uint32_t pp = uu[r] & 0xFF800000u;
       const int ee = (int)(uu[r] & 0x7F800000u);
+      const uint32_t du = uu[r] & 0x007FFFFFu;  // additive table: the uniform operand's mantissa field
 #pragma unroll
       for (int t = 0; t < TC; ++t) {
         // e = (carry << 23) + (mantissa bits << (23 - m)), AMsimulator.inl:22-23,31
         uint32_t e;
-        if (GLUT) {
+        if (LM == LM_ADD) {
+          e = du;  // entry(i, j) << (23 - m) == (i << (23 - m)) + (j << (23 - m)); the j term is in cs
+        } else if (LM == LM_GLOBAL) {
           const uint32_t v = __ldg(lut_g + ((uu[r] & rmask) | ci[t]));
           e = v * mult + (v >> 7) * cadj;
         } else {
@@ -232,7 +251,9 @@ __device__ __forceinline__ void copy_lut_to_smem(uint8_t* lut_s, const uint8_t* 
 }
 
 // Uniform operand (U): one word = sign+exponent bits | table row bits.
+template <int LM>
 __device__ __forceinline__ uint32_t enc_u(uint32_t bits, int m) {
+  if (LM == LM_ADD) return bits & ~((1u << (23 - m)) - 1u);  // sign | exponent | truncated mantissa
   return (bits & 0xFF800000u) | (((bits >> (23 - m)) & ((1u << m) - 1u)) << m);
 }
 
@@ -252,7 +273,7 @@ struct SmemLayout {
 // -----------------------------------------------------------------------------
 // gather_gemm: V gathered along k.  grid = (ceil(P/BP), ceil(Q/64), batch).
 // -----------------------------------------------------------------------------
-template <int WP, bool EXACT, bool VEC, bool CLUSTER, bool GLUT>
+template <int WP, bool EXACT, bool VEC, bool CLUSTER, int LM>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
@@ -275,7 +296,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   float* __restrict__ Og = prm.O + (long long)blockIdx.z * prm.o_bs;
   const Gather& g = prm.g;
 
-  if (!GLUT) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
 
   // ---- this thread's share of the V tile: 2 rows (p) x 2 groups of 4 k ------
   int pl[2], r0[2], c0[2];
@@ -372,10 +393,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 #pragma unroll
       for (int ip = 0; ip < 2; ++ip) {
         const float4 f = vraw[ik][ip];
-        vs[(krow + 0) * VS + pl[ip]] = enc_v<EXACT>(__float_as_uint(f.x), prm.m);
-        vs[(krow + 1) * VS + pl[ip]] = enc_v<EXACT>(__float_as_uint(f.y), prm.m);
-        vs[(krow + 2) * VS + pl[ip]] = enc_v<EXACT>(__float_as_uint(f.z), prm.m);
-        vs[(krow + 3) * VS + pl[ip]] = enc_v<EXACT>(__float_as_uint(f.w), prm.m);
+        vs[(krow + 0) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.x), prm.m);
+        vs[(krow + 1) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.y), prm.m);
+        vs[(krow + 2) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.z), prm.m);
+        vs[(krow + 3) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.w), prm.m);
       }
     }
 #pragma unroll
@@ -383,7 +404,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
       const int e = j * NT + t;
       const int kl = u_kmajor ? (e & (BK - 1)) : (e >> 6);
       const int ql = u_kmajor ? (e >> 4) : (e & 63);
-      Us[buf * BK * US + kl * US + ql] = enc_u(__float_as_uint(uraw[j]), prm.m);
+      Us[buf * BK * US + kl * US + ql] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
     }
   };
 
@@ -412,7 +433,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
     const uint32_t* us = Us + buf * BK * US + ucol;
 AMSIM_UNROLL_K
     for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT, GLUT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+      mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
                             prm.lut_raw);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
@@ -489,7 +510,7 @@ AMSIM_UNROLL_K
 // k in [s * k_chunk, min((s+1) * k_chunk, K)) and writes ws[s] (or O if there
 // is only one split).
 // -----------------------------------------------------------------------------
-template <int WP, bool EXACT, bool VEC, bool GLUT>
+template <int WP, bool EXACT, bool VEC, int LM>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
@@ -514,7 +535,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
   const float* __restrict__ Vg = prm.V;
   const float* __restrict__ Ug = prm.U;
 
-  if (!GLUT) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
 
   // ---- this thread's 4 consecutive p (same for every k row it stages) ---------
   const int pl = 4 * (t % GPR);
@@ -578,16 +599,16 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
     for (int i = 0; i < NV; ++i) {
       const float4 f = vraw[i];
       uint4 wv;
-      wv.x = enc_v<EXACT>(__float_as_uint(f.x), prm.m);
-      wv.y = enc_v<EXACT>(__float_as_uint(f.y), prm.m);
-      wv.z = enc_v<EXACT>(__float_as_uint(f.z), prm.m);
-      wv.w = enc_v<EXACT>(__float_as_uint(f.w), prm.m);
+      wv.x = enc_v<EXACT, LM>(__float_as_uint(f.x), prm.m);
+      wv.y = enc_v<EXACT, LM>(__float_as_uint(f.y), prm.m);
+      wv.z = enc_v<EXACT, LM>(__float_as_uint(f.z), prm.m);
+      wv.w = enc_v<EXACT, LM>(__float_as_uint(f.w), prm.m);
       *reinterpret_cast<uint4*>(vs + (i * RPP + krow0) * VS + pl) = wv;
     }
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
-      Us[buf * BK * US + (e >> 6) * US + (e & 63)] = enc_u(__float_as_uint(uraw[j]), prm.m);
+      Us[buf * BK * US + (e >> 6) * US + (e & 63)] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
     }
   };
 
@@ -612,7 +633,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
     const uint32_t* us = Us + buf * BK * US + ucol;
 AMSIM_UNROLL_K
     for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT, GLUT>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+      mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
                             prm.lut_raw);
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();

@@ -82,7 +82,11 @@ const char* amsim_version(void);
  * (real path, device) and reference counted; close drops one reference.
  * The file must hold exactly 2^(2m) bytes (the reference reads "up to").
  * For m <= 7 the GEMM kernels keep the table in shared memory; for m = 8..11
- * (up to 4 MiB) they look it up in global memory, where it stays L2-resident. */
+ * (up to 4 MiB) they look it up in global memory, where it stays L2-resident.
+ * A table whose entries satisfy (carry << m) + mantissa == i + j for every
+ * index pair (Mitchell's logarithmic multiplier, e.g. MIT_7) needs no lookups:
+ * the kernels add the operands' mantissa fields instead, with identical bits
+ * (set AMSIM_NO_ADDITIVE in the environment before opening to force the table). */
 int amsim_lut_open(const char* path, int device, amsim_lut** out);
 /* Same, from bytes already in host memory (m given explicitly). */
 int amsim_lut_open_bytes(const uint8_t* bytes, int m, int device, amsim_lut** out);

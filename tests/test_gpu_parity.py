@@ -607,3 +607,35 @@ def test_oversize_and_invalid_arguments_are_refused_before_any_launch(ops):
     assert b"cols of mat a" in L.amsim_last_error()
     assert L.amsim_conv2d_fwd_bias_act(None, lut.handle, P, P, None, P, 1, 4, 4, 1, 3, 3, 1, 2, 2, 1, 1, 0, 0, 7, 0) == _lib.ERR_INVALID
     torch.cuda.synchronize()
+
+
+def test_additive_table_shortcut_is_bit_identical_to_the_table_path(ops, oracle, luts, tmp_path, monkeypatch):
+    """A LUT whose encoded entries satisfy entry(i, j) == i + j (Mitchell's
+    multiplier: MIT_1/3/5/7) is served without table lookups (integer add of the
+    mantissa fields).  Same bits as the shared-memory table path and the oracle,
+    in both modes, for all three directions."""
+    import shutil
+    lut, m = luts["MIT_7"]
+    rng = np.random.default_rng(123)
+    x, wt = _conv_case(rng, 3, 11, 10, 12, 3, 3, 40)
+    g = oracle.geometry(3, 11, 10, 12, 3, 3, 40, 1, 1, "SAME")
+    dy = rng.standard_normal((3, g.out_h, g.out_w, 40)).astype(np.float32)
+    dy[dy < -0.8] = 0
+    # a second copy of the file, opened with the shortcut disabled -> table path
+    table_copy = str(tmp_path / "MITCOPY_7.bin")
+    shutil.copyfile(lut_path("MIT_7"), table_copy)
+    monkeypatch.setenv("AMSIM_NO_ADDITIVE", "1")
+    ops.get_lut(table_copy, "cuda")
+    monkeypatch.delenv("AMSIM_NO_ADDITIVE")
+    for det in (True, False):
+        outs = {}
+        for tag, path in (("add", lut_path("MIT_7")), ("table", table_copy)):
+            kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=path, deterministic=det)
+            outs[tag] = (ops.convam(dev(x), dev(wt), **kw_), ops.convam_filter_grad(wt.shape, dev(x), dev(dy), **kw_),
+                         ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_))
+        for a, b in zip(outs["add"], outs["table"]):
+            assert torch.equal(a, b), det
+        if det:
+            assert_bit_equal(outs["add"][0].cpu().numpy(), oracle.conv2d_fwd(g, x, wt, lut, m), "additive fwd")
+            assert_bit_equal(outs["add"][1].cpu().numpy(), oracle.conv2d_bwd_filter(g, x, dy, lut, m), "additive fgrad")
+            assert_bit_equal(outs["add"][2].cpu().numpy(), oracle.conv2d_bwd_input(g, wt, dy, lut, m), "additive igrad")
