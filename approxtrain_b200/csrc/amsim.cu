@@ -12,7 +12,9 @@
 
 #include <map>
 #include <mutex>
+#include <set>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #ifndef AMSIM_CTAS1
@@ -196,33 +198,117 @@ void fill_gather_divs(Gather& g) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Resident CTA slots of a 128-thread kernel on the whole device (occupancy x multiprocessors);
+// looked up once per kernel, device and shared-memory size.
+template <typename Kern>
+int resident_slots(Kern kern, size_t smem, int device, int* out) {
+  static std::mutex mu;
+  static std::map<std::tuple<const void*, int, size_t>, int> known;
+  std::lock_guard<std::mutex> lk(mu);
+  auto key = std::make_tuple((const void*)kern, device, smem);
+  auto it = known.find(key);
+  if (it == known.end()) {
+    int per_sm = 0, sms = 0;
+    CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 128, smem));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    it = known.emplace(key, per_sm * sms).first;
+  }
+  *out = it->second;
+  return AMSIM_OK;
+}
+
+// Stream-ordered scratch for the balanced launch: the pool keeps freed blocks, so after the
+// first call this neither synchronises nor reaches the driver's allocator.
+int scratch_alloc(cudaStream_t st, int device, size_t bytes, float** out) {
+  static std::mutex mu;
+  static std::set<int> tuned;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!tuned.count(device)) {
+      cudaMemPool_t pool;
+      CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, device));
+      uint64_t keep = ~0ull;
+      CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+      tuned.insert(device);
+    }
+  }
+  CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(out), bytes, st));
+  return AMSIM_OK;
+}
+
 template <bool EXACT, bool VEC, int LM>
 int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   using L = SmemLayout<1>;
   const int ptiles = (p.P + L::BP - 1) / L::BP, qtiles = (p.Q + BQ - 1) / BQ;
-  // Fast mode: when the tiles alone cannot fill the resident CTA slots, a
-  // thread-block cluster of `ksplit` CTAs shares each tile's reduction.
+  const long long ctas = (long long)ptiles * qtiles * batch;
+  const int nkb = (p.K + BK - 1) / BK;
+  p.ksplit = 1;
+  p.tile_bytes = L::TILE_BYTES;
+  const size_t smem_plain = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
+
+  // Fast mode, balanced launch: the plain grid would leave the last wave of resident CTA slots
+  // partly empty (or never fill them), so the (tile, reduction block) pairs are dealt out in
+  // equal runs to exactly as many CTAs as the device holds.  Not taken while the stream is
+  // being captured into a graph (the scratch comes from the stream-ordered allocator).
+  if constexpr (!EXACT) {
+    int rc = ensure_smem(gather_gemm<1, EXACT, VEC, GM_BALANCED, LM>, smem_plain, device);
+    if (rc) return rc;
+    int slots = 0;
+    rc = resident_slots(gather_gemm<1, EXACT, VEC, GM_BALANCED, LM>, smem_plain, device, &slots);
+    if (rc) return rc;
+    const long long iters = ctas * nkb;
+    const long long waves = (ctas + slots - 1) / slots;
+    const double fill = (double)ctas / (double)(waves * slots);
+    long long grid = slots;
+    if (iters / grid < 8) grid = iters / 8;  // at least 8 reduction blocks per CTA
+    // measured: pays when the plain grid is at most two waves with a last wave under ~93 % full
+    // (one wave at 88 %: -7 %); with more waves the plain grid's tail is already short
+    int mode = waves <= 2 && fill < 0.93 && grid >= 2 && nkb >= 2;
+    if (const char* f = getenv("AMSIM_BALANCED")) mode = atoi(f) != 0 && grid >= 1;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    CUDA_TRY(cudaStreamIsCapturing(st, &cap));
+    if (mode && cap == cudaStreamCaptureStatusNone && slots > 0) {
+      p.sk_iters = iters;
+      p.sk_ptiles = ptiles;
+      p.sk_qtiles = qtiles;
+      p.sk_grid = (int)grid;
+      const size_t bytes = (size_t)grid * 2 * TR * TC * L::NT * sizeof(float);
+      rc = scratch_alloc(st, device, bytes, &p.ws);
+      if (rc) return rc;
+      gather_gemm<1, EXACT, VEC, GM_BALANCED, LM><<<dim3((unsigned)grid), L::NT, smem_plain, st>>>(p);
+      cudaError_t e1 = cudaGetLastError();
+      if (e1 == cudaSuccess) {
+        gather_combine<1><<<dim3((unsigned)ctas), L::NT, 0, st>>>(p);
+        e1 = cudaGetLastError();
+      }
+      cudaError_t e2 = cudaFreeAsync(p.ws, st);
+      p.ws = nullptr;
+      CUDA_TRY(e1);
+      CUDA_TRY(e2);
+      return AMSIM_OK;
+    }
+  }
+
+  // Fast mode, small launches inside a graph capture: a thread-block cluster of `ksplit` CTAs
+  // shares each tile's reduction when the tiles alone cannot fill the resident CTA slots.
   int ksplit = 1;
   if (!EXACT && LM != LM_GLOBAL) {
-    const long long ctas = (long long)ptiles * qtiles * batch;
     const int slots = 148 * AMSIM_CTAS1;
-    const int nkb = (p.K + BK - 1) / BK;
     while (ksplit < 8 && ctas * (ksplit * 2) <= slots && nkb / (ksplit * 2) >= 6) ksplit *= 2;
     if (const char* f = getenv("AMSIM_FORCE_KSPLIT")) ksplit = atoi(f) > 0 ? atoi(f) : 1;
   }
   p.ksplit = ksplit;
-  p.tile_bytes = L::TILE_BYTES;
   if (ksplit > 1 && L::EXCHANGE_BYTES > p.tile_bytes) p.tile_bytes = L::EXCHANGE_BYTES;
   const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
   if (ksplit == 1) {
-    int rc = ensure_smem(gather_gemm<1, EXACT, VEC, false, LM>, smem, device);
+    int rc = ensure_smem(gather_gemm<1, EXACT, VEC, GM_PLAIN, LM>, smem, device);
     if (rc) return rc;
-    gather_gemm<1, EXACT, VEC, false, LM><<<dim3(ptiles, qtiles, batch), L::NT, smem, st>>>(p);
+    gather_gemm<1, EXACT, VEC, GM_PLAIN, LM><<<dim3(ptiles, qtiles, batch), L::NT, smem, st>>>(p);
     CUDA_TRY(cudaGetLastError());
     return AMSIM_OK;
   }
-  constexpr bool kCanCluster = !EXACT && LM != LM_GLOBAL;
-  int rc = ensure_smem(gather_gemm<1, EXACT, VEC, kCanCluster, LM>, smem, device);
+  constexpr int kClusterMode = (!EXACT && LM != LM_GLOBAL) ? GM_CLUSTER : GM_PLAIN;
+  int rc = ensure_smem(gather_gemm<1, EXACT, VEC, kClusterMode, LM>, smem, device);
   if (rc) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -237,10 +323,9 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, gather_gemm<1, EXACT, VEC, kCanCluster, LM>, p));
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, gather_gemm<1, EXACT, VEC, kClusterMode, LM>, p));
   return AMSIM_OK;
 }
-
 int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device) {
   if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
   if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");

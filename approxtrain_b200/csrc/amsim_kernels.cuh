@@ -137,6 +137,12 @@ struct Params {
   // fgrad only
   int k_chunk, splits;
   float* ws;                    // [splits][P][Q] partial sums when splits > 1
+  // gather_gemm, balanced mode: the (tile, reduction block) pairs of the whole problem are
+  // dealt out in equal contiguous runs to the CTAs of a grid that exactly fills the GPU; a tile
+  // whose reduction is shared between CTAs goes through `ws` (two register-tile slots per CTA)
+  long long sk_iters;           // tiles * reduction blocks per tile
+  int sk_ptiles, sk_qtiles;     // tile grid (q runs fastest, then p, then batch)
+  int sk_grid;                  // CTAs of the balanced launch
 };
 
 __device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
@@ -148,6 +154,11 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
+
+// How gather_gemm spreads the reduction.
+constexpr int GM_PLAIN = 0;     // one CTA per tile, whole reduction
+constexpr int GM_CLUSTER = 1;   // a thread-block cluster shares a tile's reduction
+constexpr int GM_BALANCED = 2;  // equal runs of (tile, reduction block) per CTA, partial tiles via workspace
 
 // Where the products' table bits come from.
 constexpr int LM_SMEM = 0;    // 2^m x 2^m byte table in shared memory (m <= 7)
@@ -273,11 +284,59 @@ struct SmemLayout {
 // -----------------------------------------------------------------------------
 // gather_gemm: V gathered along k.  grid = (ceil(P/BP), ceil(Q/64), batch).
 // -----------------------------------------------------------------------------
-template <int WP, bool EXACT, bool VEC, bool CLUSTER, int LM>
+// Writes one thread's 16 (q) x 4 (p) register tile: out = act(acc + bias[q]) at Out[row(p), q].
+__device__ __forceinline__ void store_out_tile(const Params& prm, float (&acc)[TR][TC], float* __restrict__ Og,
+                                               const int prow0, const int qcol0) {
+  const Gather& g = prm.g;
+  const bool vec_out = prm.o_sq == 1 && (prm.o_sp & 3) == 0 && (prm.o_bs & 3) == 0 &&
+                       ((reinterpret_cast<uintptr_t>(prm.O) & 15) == 0);
+#pragma unroll
+  for (int c = 0; c < TC; ++c) {
+    const int pg = prow0 + c;
+    if (pg >= prm.P) continue;
+    long long row = pg;
+    if (prm.o_strided) {
+      const uint32_t n = fdiv((uint32_t)pg, g.d_img);
+      const uint32_t rem = (uint32_t)pg - n * (uint32_t)(g.PH * g.PW);
+      const uint32_t yy = fdiv(rem, g.d_pw);
+      const uint32_t xx = rem - yy * (uint32_t)g.PW;
+      row = ((long long)n * prm.o_h + (long long)yy * prm.o_sh + prm.o_a) * prm.o_w + (long long)xx * prm.o_sw + prm.o_b;
+    }
+    float* orow = Og + row * prm.o_sp;
+#pragma unroll
+    for (int g4 = 0; g4 < TR / 4; ++g4) {
+      const int qg = qcol0 + 4 * g4;
+      float o[4] = {acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]};
+      if (prm.bias != nullptr || prm.relu) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          if (prm.bias != nullptr && qg + r < prm.Q) o[r] = __fadd_rn(o[r], __ldg(prm.bias + qg + r));
+          if (prm.relu) o[r] = o[r] < 0.f ? 0.f : o[r];
+        }
+      }
+      if (vec_out && qg + 3 < prm.Q) {
+        *reinterpret_cast<float4*>(orow + qg) = make_float4(o[0], o[1], o[2], o[3]);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          if (qg + r < prm.Q) orow[(long long)(qg + r) * prm.o_sq] = o[r];
+      }
+    }
+  }
+}
+
+// First reduction block of CTA c in a balanced launch of `grid` CTAs over `iters` blocks.
+__device__ __forceinline__ long long balanced_begin(long long c, long long iters, int grid) {
+  return c * iters / grid;
+}
+
+template <int WP, bool EXACT, bool VEC, int MODE, int LM>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
   constexpr int NU = BK * BQ / NT;  // U elements staged per thread
+  constexpr bool CLUSTER = MODE == GM_CLUSTER;
+  constexpr bool BALANCED = MODE == GM_BALANCED;
 
   extern __shared__ __align__(16) uint8_t smem[];
   uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);
@@ -290,13 +349,41 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   const int wp = w % WP, wq = w / WP;
   const int ksplit = CLUSTER ? prm.ksplit : 1;   // cluster size along x
   const int krank = blockIdx.x % ksplit;         // this CTA's slice of the reduction
-  const int p0 = (blockIdx.x / ksplit) * BP, q0 = blockIdx.y * BQ;
-  const float* __restrict__ Vg = prm.V + (long long)blockIdx.z * prm.v_bs;
-  const float* __restrict__ Ug = prm.U + (long long)blockIdx.z * prm.u_bs;
-  float* __restrict__ Og = prm.O + (long long)blockIdx.z * prm.o_bs;
   const Gather& g = prm.g;
+  const int nkb_all = (prm.K + BK - 1) / BK;
 
   if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+
+  // Balanced mode: this CTA's run of (tile, reduction block) pairs; otherwise one pass.
+  long long run_at = 0, run_end = 0;
+  if (BALANCED) {
+    run_at = balanced_begin(blockIdx.x, prm.sk_iters, prm.sk_grid);
+    run_end = balanced_begin((long long)blockIdx.x + 1, prm.sk_iters, prm.sk_grid);
+    if (run_at >= run_end) return;
+  }
+  do {
+  int tile_p, tile_q, tile_z, kb_begin, nkb;
+  if (BALANCED) {
+    const long long tile = run_at / nkb_all;
+    kb_begin = (int)(run_at - tile * nkb_all);
+    nkb = kb_begin + (int)min((long long)(nkb_all - kb_begin), run_end - run_at);
+    run_at += nkb - kb_begin;
+    tile_q = (int)(tile % prm.sk_qtiles);
+    const long long rest = tile / prm.sk_qtiles;
+    tile_p = (int)(rest % prm.sk_ptiles);
+    tile_z = (int)(rest / prm.sk_ptiles);
+  } else {
+    tile_p = blockIdx.x / ksplit;
+    tile_q = blockIdx.y;
+    tile_z = blockIdx.z;
+    const int per = (nkb_all + ksplit - 1) / ksplit;
+    kb_begin = krank * per;
+    nkb = min(kb_begin + per, nkb_all);
+  }
+  const int p0 = tile_p * BP, q0 = tile_q * BQ;
+  const float* __restrict__ Vg = prm.V + (long long)tile_z * prm.v_bs;
+  const float* __restrict__ Ug = prm.U + (long long)tile_z * prm.u_bs;
+  float* __restrict__ Og = prm.O + (long long)tile_z * prm.o_bs;
 
   // ---- this thread's share of the V tile: 2 rows (p) x 2 groups of 4 k ------
   int pl[2], r0[2], c0[2];
@@ -414,10 +501,6 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 #pragma unroll
     for (int c = 0; c < TC; ++c) acc[r][c] = 0.f;
 
-  const int nkb_all = (prm.K + BK - 1) / BK;
-  const int per = (nkb_all + ksplit - 1) / ksplit;
-  const int kb_begin = krank * per;
-  const int nkb = min(kb_begin + per, nkb_all);
   if (kb_begin < nkb) {
     load_tile(kb_begin);
     store_tile(0);
@@ -425,7 +508,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   __syncthreads();
 
   const int vcol = wp * 128 + 4 * lane;
-  const int ucol = wq * TR;
+  // broadcast from lane 0: tells the compiler the uniform operand's address is warp-uniform
+  const int ucol = __shfl_sync(0xffffffffu, wq, 0) * TR;
   for (int kb = kb_begin; kb < nkb; ++kb) {
     const int buf = (kb - kb_begin) & 1;
     if (kb + 1 < nkb) load_tile(kb + 1);
@@ -465,42 +549,57 @@ AMSIM_UNROLL_K
     if (krank != 0) return;
   }
 
-  // ---- epilogue ---------------------------------------------------------------
-  const bool vec_out = prm.o_sq == 1 && (prm.o_sp & 3) == 0 && (prm.o_bs & 3) == 0 &&
-                       ((reinterpret_cast<uintptr_t>(prm.O) & 15) == 0);
+  // ---- balanced mode: a tile whose reduction this CTA only shares parks its register
+  // tile in the workspace (slot 0: the run started inside the tile, slot 1: it started the tile)
+  if (BALANCED && (kb_begin != 0 || nkb != nkb_all)) {
+    float* slot = prm.ws + ((long long)blockIdx.x * 2 + (kb_begin == 0 ? 1 : 0)) * (TR * TC * NT);
 #pragma unroll
-  for (int c = 0; c < TC; ++c) {
-    const int pg = p0 + vcol + c;
-    if (pg >= prm.P) continue;
-    long long row = pg;
-    if (prm.o_strided) {
-      const uint32_t n = fdiv((uint32_t)pg, g.d_img);
-      const uint32_t rem = (uint32_t)pg - n * (uint32_t)(g.PH * g.PW);
-      const uint32_t yy = fdiv(rem, g.d_pw);
-      const uint32_t xx = rem - yy * (uint32_t)g.PW;
-      row = ((long long)n * prm.o_h + yy * prm.o_sh + prm.o_a) * prm.o_w + xx * prm.o_sw + prm.o_b;
-    }
-    float* orow = Og + row * prm.o_sp;
+    for (int r = 0; r < TR; ++r)
 #pragma unroll
-    for (int g4 = 0; g4 < TR / 4; ++g4) {
-      const int qg = q0 + ucol + 4 * g4;
-      float o[4] = {acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]};
-      if (prm.bias != nullptr || prm.relu) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          if (prm.bias != nullptr && qg + r < prm.Q) o[r] = __fadd_rn(o[r], __ldg(prm.bias + qg + r));
-          if (prm.relu) o[r] = o[r] < 0.f ? 0.f : o[r];
-        }
-      }
-      if (vec_out && qg + 3 < prm.Q) {
-        *reinterpret_cast<float4*>(orow + qg) = make_float4(o[0], o[1], o[2], o[3]);
-      } else {
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-          if (qg + r < prm.Q) orow[(long long)(qg + r) * prm.o_sq] = o[r];
-      }
-    }
+      for (int c = 0; c < TC; ++c) slot[(r * TC + c) * NT + t] = acc[r][c];
+  } else {
+    store_out_tile(prm, acc, Og, p0 + vcol, q0 + ucol);
   }
+  } while (BALANCED && run_at < run_end);
+}
+
+// Second pass of a balanced gather_gemm launch: one CTA per tile adds the parked register
+// tiles of the CTAs that shared the tile's reduction, in CTA order, and writes the output.
+// Tiles reduced by a single CTA were written by gather_gemm itself.
+template <int WP>
+__global__ void __launch_bounds__(WP * 128) gather_combine(const Params prm) {
+  using L = SmemLayout<WP>;
+  constexpr int NT = L::NT, BP = L::BP;
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  const int wp = w % WP, wq = w / WP;
+  const int nkb_all = (prm.K + BK - 1) / BK;
+  const long long tile = blockIdx.x;
+  const long long first = tile * nkb_all, last = first + nkb_all;
+  long long c = first * prm.sk_grid / prm.sk_iters;
+  while (c > 0 && balanced_begin(c, prm.sk_iters, prm.sk_grid) > first) --c;
+  while (balanced_begin(c + 1, prm.sk_iters, prm.sk_grid) <= first) ++c;
+  if (balanced_begin(c + 1, prm.sk_iters, prm.sk_grid) >= last) return;  // one CTA had the whole tile
+
+  float acc[TR][TC];
+#pragma unroll
+  for (int r = 0; r < TR; ++r)
+#pragma unroll
+    for (int k = 0; k < TC; ++k) acc[r][k] = 0.f;
+  for (; c < prm.sk_grid; ++c) {
+    const long long b = balanced_begin(c, prm.sk_iters, prm.sk_grid);
+    if (b >= last) break;
+    if (balanced_begin(c + 1, prm.sk_iters, prm.sk_grid) == b) continue;  // empty run
+    const float* slot = prm.ws + (c * 2 + (b <= first ? 1 : 0)) * (TR * TC * NT);
+#pragma unroll
+    for (int r = 0; r < TR; ++r)
+#pragma unroll
+      for (int k = 0; k < TC; ++k) acc[r][k] = __fadd_rn(acc[r][k], slot[(r * TC + k) * NT + t]);
+  }
+  const int tile_q = (int)(tile % prm.sk_qtiles);
+  const long long rest = tile / prm.sk_qtiles;
+  const int tile_p = (int)(rest % prm.sk_ptiles), tile_z = (int)(rest / prm.sk_ptiles);
+  float* __restrict__ Og = prm.O + (long long)tile_z * prm.o_bs;
+  store_out_tile(prm, acc, Og, tile_p * BP + wp * 128 + 4 * lane, tile_q * BQ + wq * TR);
 }
 
 // -----------------------------------------------------------------------------

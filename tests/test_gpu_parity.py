@@ -367,6 +367,7 @@ def test_cluster_split_of_the_reduction(ops, oracle, luts, force, monkeypatch):
     x, wt = _conv_case(rng, 2, 7, 7, 64, 3, 3, 96)          # 98 pixels, 2 channel tiles, K = 576 (36 stages)
     g = oracle.geometry(2, 7, 7, 64, 3, 3, 96, 1, 1, "SAME")
     dy = rng.standard_normal((2, 7, 7, 96)).astype(np.float32)
+    monkeypatch.setenv("AMSIM_BALANCED", "0")  # outside a graph capture the balanced launch would take this shape
     if force is not None:
         monkeypatch.setenv("AMSIM_FORCE_KSPLIT", force)
     kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=lut_path("MBM_7"))
@@ -378,6 +379,55 @@ def test_cluster_split_of_the_reduction(ops, oracle, luts, force, monkeypatch):
     assert np.array_equal(y, y2), "rank-ordered combine: run-to-run identical"
     yd = ops.convam(dev(x), dev(wt), deterministic=True, **kw_).cpu().numpy()
     assert_bit_equal(yd, oracle.conv2d_fwd(g, x, wt, lut, m), "deterministic mode ignores the split")
+
+
+@pytest.mark.parametrize("balanced", [None, "1", "0"])
+def test_balanced_launch_of_the_reduction(ops, oracle, luts, balanced, monkeypatch, tmp_path):
+    """Fast mode deals the (tile, reduction block) pairs out in equal runs to as many
+    CTAs as the device holds; tiles shared between CTAs are combined in CTA order by a
+    second pass.  Forced on ("1"), off ("0") and chosen by the library (None): same
+    parity bar, run-to-run identical, every epilogue (strided output rows of a
+    stride-2 input gradient, bias + ReLU, batched matmul) and every table mode."""
+    if balanced is not None:
+        monkeypatch.setenv("AMSIM_BALANCED", balanced)
+    lut, m = luts["MBM_7"]
+    p7 = lut_path("MBM_7")
+    rng = np.random.default_rng(77)
+    cases = [(2, 7, 7, 64, 3, 3, 96, 1, "SAME"),      # 2 tiles, 36 reduction blocks
+             (3, 20, 20, 32, 3, 3, 70, 1, "SAME"),    # 10 x 2 tiles, ragged in p and q
+             (2, 15, 15, 16, 3, 3, 24, 2, "SAME"),    # stride 2: input gradient by stride phase
+             (1, 12, 12, 3, 5, 5, 6, 2, "VALID")]     # scalar gather path
+    for (n, h, w, c, kh, kw, k, s, pad) in cases:
+        x, wt = _conv_case(rng, n, h, w, c, kh, kw, k)
+        g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+        dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+        b = rng.standard_normal(k).astype(np.float32)
+        kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=p7)
+        y = ops.convam(dev(x), dev(wt), **kw_)
+        assert_close(y.cpu().numpy(), oracle.conv2d_fwd(g, x, wt, lut, m), f"balanced fwd {balanced}")
+        assert torch.equal(y, ops.convam(dev(x), dev(wt), **kw_)), "run-to-run identical"
+        dx = ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_).cpu().numpy()
+        assert_close(dx, oracle.conv2d_bwd_input(g, wt, dy, lut, m), f"balanced input-grad {balanced}")
+        fused = ops.convam_bias_act(dev(x), dev(wt), dev(b), activation="relu", **kw_)
+        assert torch.equal(fused, torch.relu(y + dev(b))), "epilogue after the combine"
+    a = rng.standard_normal((5, 40, 200)).astype(np.float32)
+    bb = rng.standard_normal((5, 200, 70)).astype(np.float32)
+    c_ = ops.matmulam(dev(a), dev(bb), mant_mul_lut=p7).cpu().numpy()
+    assert_close(c_, oracle.matmul(a, bb, lut, m), f"balanced batched matmul {balanced}")
+    # additive table (no lookup) and a table in global memory
+    x, wt = _conv_case(rng, 2, 9, 9, 32, 3, 3, 40)
+    g = oracle.geometry(2, 9, 9, 32, 3, 3, 40, 1, 1, "SAME")
+    lutm, mm = luts["MIT_7"]
+    ym = ops.convam(dev(x), dev(wt), strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=lut_path("MIT_7")).cpu().numpy()
+    assert_close(ym, oracle.conv2d_fwd(g, x, wt, lutm, mm), f"balanced additive {balanced}")
+    lut9 = rng.integers(0, 256, size=1 << 18, dtype=np.uint8)
+    path9 = str(tmp_path / "RAND_9.bin")
+    lut9.tofile(path9)
+    y9 = ops.convam(dev(x), dev(wt), strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=path9).cpu().numpy()
+    assert_close(y9, oracle.conv2d_fwd(g, x, wt, lut9, 9), f"balanced global table {balanced}")
+    # deterministic mode never splits a reduction
+    yd = ops.convam(dev(x), dev(wt), strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=p7, deterministic=True).cpu().numpy()
+    assert_bit_equal(yd, oracle.conv2d_fwd(g, x, wt, lut, m), "deterministic mode ignores the balanced launch")
 
 
 @pytest.mark.parametrize("m", [8, 9, 11])
