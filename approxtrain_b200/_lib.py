@@ -22,11 +22,12 @@ STATIC_SCRATCH_BYTES = 8 << 20
 EXPORTS = [
     "amsim_last_error", "amsim_version", "amsim_lut_open", "amsim_lut_open_bytes", "amsim_lut_close",
     "amsim_lut_info", "amsim_mul", "amsim_conv2d_geometry", "amsim_conv2d_fwd", "amsim_conv2d_fwd_bias_act",
-    "amsim_dense_fwd_bias_act", "amsim_conv2d_bwd_input",
+    "amsim_dense_fwd_bias_act", "amsim_conv2d_fwd_scale_bias_act", "amsim_conv2d_bwd_input",
     "amsim_conv2d_bwd_filter_workspace", "amsim_conv2d_bwd_filter", "amsim_conv2d_bwd_filter_static",
     "amsim_dense_fwd",
     "amsim_dense_bwd_weight_workspace", "amsim_dense_bwd_weight", "amsim_dense_bwd_input", "amsim_matmul",
-    "amsim_debug_fastdiv",
+    "amsim_matmul_ex",
+    "amsim_debug_fastdiv", "amsim_debug_launch_count",
 ]
 
 
@@ -56,6 +57,7 @@ def _load() -> C.CDLL:
     L.amsim_conv2d_fwd.argtypes = [vp, vp, fp, fp, fp] + conv_dims + [u]
     L.amsim_conv2d_fwd_bias_act.argtypes = [vp, vp, fp, fp, fp, fp] + conv_dims + [ip, u]
     L.amsim_dense_fwd_bias_act.argtypes = [vp, vp, fp, fp, fp, fp, ip, ip, ip, ip, u]
+    L.amsim_conv2d_fwd_scale_bias_act.argtypes = [vp, vp, fp, fp, fp, fp, fp] + conv_dims + [ip, u]
     L.amsim_conv2d_bwd_input.argtypes = [vp, vp, fp, fp, fp] + conv_dims + [u]
     L.amsim_conv2d_bwd_filter_workspace.argtypes = [ip] * 9 + [u]
     L.amsim_conv2d_bwd_filter_workspace.restype = sz
@@ -67,8 +69,11 @@ def _load() -> C.CDLL:
     L.amsim_dense_bwd_weight.argtypes = [vp, vp, fp, fp, fp, ip, ip, ip, vp, sz, u]
     L.amsim_dense_bwd_input.argtypes = [vp, vp, fp, fp, fp, ip, ip, ip, u]
     L.amsim_matmul.argtypes = [vp, vp, fp, fp, fp] + [ip] * 6 + [u]
+    L.amsim_matmul_ex.argtypes = [vp, vp, fp, fp, fp] + [ip] * 8 + [C.POINTER(C.c_float), u]
     L.amsim_debug_fastdiv.argtypes = [C.c_uint32, C.c_uint32]
     L.amsim_debug_fastdiv.restype = C.c_uint32
+    L.amsim_debug_launch_count.argtypes = []
+    L.amsim_debug_launch_count.restype = C.c_ulonglong
     return L
 
 

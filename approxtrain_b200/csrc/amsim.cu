@@ -22,6 +22,12 @@
 #endif
 #include "amsim_kernels.cuh"
 
+#include <atomic>
+
+// Kernels launched by this library since it was loaded (amsim_debug_launch_count).
+static std::atomic<unsigned long long> g_launches{0};
+#define AMSIM_COUNT_LAUNCH() g_launches.fetch_add(1, std::memory_order_relaxed)
+
 using namespace amsim;
 
 namespace {
@@ -275,9 +281,11 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
       const size_t bytes = (size_t)grid * 2 * TR * TC * L::NT * sizeof(float);
       rc = scratch_alloc(st, device, bytes, &p.ws);
       if (rc) return rc;
+      AMSIM_COUNT_LAUNCH();
       gather_gemm<1, EXACT, VEC, GM_BALANCED, LM><<<dim3((unsigned)grid), L::NT, smem_plain, st>>>(p);
       cudaError_t e1 = cudaGetLastError();
       if (e1 == cudaSuccess) {
+        AMSIM_COUNT_LAUNCH();
         gather_combine<1><<<dim3((unsigned)ctas), L::NT, 0, st>>>(p);
         e1 = cudaGetLastError();
       }
@@ -303,6 +311,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   if (ksplit == 1) {
     int rc = ensure_smem(gather_gemm<1, EXACT, VEC, GM_PLAIN, LM>, smem, device);
     if (rc) return rc;
+    AMSIM_COUNT_LAUNCH();
     gather_gemm<1, EXACT, VEC, GM_PLAIN, LM><<<dim3(ptiles, qtiles, batch), L::NT, smem, st>>>(p);
     CUDA_TRY(cudaGetLastError());
     return AMSIM_OK;
@@ -323,13 +332,14 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
+  AMSIM_COUNT_LAUNCH();
   CUDA_TRY(cudaLaunchKernelEx(&cfg, gather_gemm<1, EXACT, VEC, kClusterMode, LM>, p));
   return AMSIM_OK;
 }
 int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device) {
   if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
   if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");
-  const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
+  const bool vec = !p.v_trans && (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
 #define AMSIM_GO(EX_, VEC_, LM_) return launch_gather_t<EX_, VEC_, LM_>(st, p, batch, device)
 #define AMSIM_GO_LM(LM_)                                                                        \
   do {                                                                                          \
@@ -378,14 +388,35 @@ int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   int rc = ensure_smem(fgrad_gemm<1, EXACT, VEC, LM>, smem, device);
   if (rc) return rc;
   dim3 grid((p.P + L::BP - 1) / L::BP, (p.Q + BQ - 1) / BQ, p.splits);
+  AMSIM_COUNT_LAUNCH();
   fgrad_gemm<1, EXACT, VEC, LM><<<grid, L::NT, smem, st>>>(p);
   CUDA_TRY(cudaGetLastError());
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
+    AMSIM_COUNT_LAUNCH();
     reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits);
     CUDA_TRY(cudaGetLastError());
   }
   return AMSIM_OK;
+}
+
+template <int TQ, int LM>
+int launch_fgrad_thin_t(cudaStream_t st, Params& p, int device) {
+  p.tile_bytes = (2 * THIN_BK * 32 + 2 * THIN_BK * 4 * TQ) * 4;
+  const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
+  int rc = ensure_smem(fgrad_exact_thin<TQ, LM>, smem, device);
+  if (rc) return rc;
+  dim3 grid((p.P + 31) / 32, (p.Q + 4 * TQ - 1) / (4 * TQ), 1);
+  AMSIM_COUNT_LAUNCH();
+  fgrad_exact_thin<TQ, LM><<<grid, 128, smem, st>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  return AMSIM_OK;
+}
+template <int LM>
+int launch_fgrad_thin(cudaStream_t st, Params& p, int tq, int device) {
+  if (tq == 4) return launch_fgrad_thin_t<4, LM>(st, p, device);
+  if (tq == 2) return launch_fgrad_thin_t<2, LM>(st, p, device);
+  return launch_fgrad_thin_t<1, LM>(st, p, device);
 }
 
 int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_bytes, int device) {
@@ -399,6 +430,21 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   p.splits = f.splits;
   p.k_chunk = f.k_chunk;
   p.ws = static_cast<float*>(ws);
+  if (exact) {
+    // Deterministic mode cannot split a reduction; when the 128 x 64 tiles would fill less than
+    // half of the resident CTA slots, threads take fewer chains each so the whole device works.
+    const long long fat = (long long)((p.P + 127) / 128) * ((p.Q + BQ - 1) / BQ);
+    const long long chains = (long long)p.P * p.Q;
+    int thin = fat * 2 < 148 * AMSIM_CTAS1;
+    if (const char* e = getenv("AMSIM_THIN_FGRAD")) thin = atoi(e) != 0;
+    if (thin) {
+      int tq = chains >= 4ll * 32 * 4 * 148 * 2 ? 4 : chains >= 2ll * 32 * 4 * 148 * 2 ? 2 : 1;
+      if (const char* e = getenv("AMSIM_THIN_TQ")) tq = atoi(e);
+      if (p.lut_mode == LM_ADD) return launch_fgrad_thin<LM_ADD>(st, p, tq, device);
+      if (p.lut_mode == LM_GLOBAL) return launch_fgrad_thin<LM_GLOBAL>(st, p, tq, device);
+      return launch_fgrad_thin<LM_SMEM>(st, p, tq, device);
+    }
+  }
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
 #define AMSIM_GO(EX_, VEC_, LM_) return launch_fgrad_t<EX_, VEC_, LM_>(st, p, device)
 #define AMSIM_GO_LM(LM_)                                                                        \
@@ -419,6 +465,7 @@ int launch_naive_i32(cudaStream_t st, Params& p, const amsim_lut* lut, bool fgra
   p.lut_raw = lut->d_raw;  // rows by the first operand; v_first tells the kernel which operand that is
   const long long n = (long long)p.P * p.Q;
   const unsigned blocks = (unsigned)((n + 127) / 128);
+  AMSIM_COUNT_LAUNCH();
   if (fgrad)
     naive_fgrad_i32<<<blocks, 128, 0, st>>>(p);
   else
@@ -446,6 +493,8 @@ extern "C" {
 const char* amsim_last_error(void) { return g_err; }
 
 const char* amsim_version(void) { return "amsim 0.1 (sm_100a)"; }
+
+unsigned long long amsim_debug_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 uint32_t amsim_debug_fastdiv(uint32_t n, uint32_t d) { return fdiv(n, make_fastdiv(d)); }
 
@@ -523,6 +572,7 @@ int amsim_mul(void* stream, const amsim_lut* lut, const float* a, const float* b
   if (!a || !b || !out) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   size_t blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
+  AMSIM_COUNT_LAUNCH();
   mul_elementwise<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, lut->d_raw, lut->m);
   CUDA_TRY(cudaGetLastError());
   return AMSIM_OK;
@@ -554,13 +604,13 @@ int amsim_conv2d_geometry(int in_h, int in_w, int f_h, int f_w, int stride_h, in
   return AMSIM_OK;
 }
 
-static int conv2d_fwd_impl(void* stream, const amsim_lut* lut, const float* x, const float* w, const float* bias,
-                           float* y, int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
+static int conv2d_fwd_impl(void* stream, const amsim_lut* lut, const float* x, const float* w, const float* scale,
+                           const float* bias, float* y, int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
                            int out_w, int stride_h, int stride_w, int pad_top, int pad_left, int act, unsigned flags) {
   int rc = check_common(lut, flags, true);
   if (rc) return rc;
   if (act != AMSIM_ACT_NONE && act != AMSIM_ACT_RELU) return fail(AMSIM_ERR_INVALID, "unknown activation %d", act);
-  if ((bias || act) && (flags & AMSIM_INT32)) return fail(AMSIM_ERR_UNSUPPORTED, "the fused epilogue is FP32 only");
+  if ((bias || scale || act) && (flags & AMSIM_INT32)) return fail(AMSIM_ERR_UNSUPPORTED, "the fused epilogue is FP32 only");
   rc = check_conv_dims(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h, stride_w, pad_top, pad_left);
   if (rc) return rc;
   if (batch == 0 || out_h == 0 || out_w == 0) return AMSIM_OK;
@@ -576,6 +626,7 @@ static int conv2d_fwd_impl(void* stream, const amsim_lut* lut, const float* x, c
   p.o_sp = out_c; p.o_sq = 1;
   fill_lut(p, lut, /*v_is_first_operand=*/true);
   p.bias = bias;
+  p.scale = scale;
   p.relu = act == AMSIM_ACT_RELU;
   if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, false);
   return launch_gather((cudaStream_t)stream, p, 1, flags & AMSIM_DETERMINISTIC, lut->device);
@@ -584,16 +635,24 @@ static int conv2d_fwd_impl(void* stream, const amsim_lut* lut, const float* x, c
 int amsim_conv2d_fwd(void* stream, const amsim_lut* lut, const float* x, const float* w, float* y, int batch, int in_h,
                      int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w, int stride_h, int stride_w,
                      int pad_top, int pad_left, unsigned flags) {
-  return conv2d_fwd_impl(stream, lut, x, w, nullptr, y, batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h,
-                         stride_w, pad_top, pad_left, AMSIM_ACT_NONE, flags);
+  return conv2d_fwd_impl(stream, lut, x, w, nullptr, nullptr, y, batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w,
+                         stride_h, stride_w, pad_top, pad_left, AMSIM_ACT_NONE, flags);
 }
 
 int amsim_conv2d_fwd_bias_act(void* stream, const amsim_lut* lut, const float* x, const float* w, const float* bias,
                               float* y, int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
                               int out_w, int stride_h, int stride_w, int pad_top, int pad_left, int act,
                               unsigned flags) {
-  return conv2d_fwd_impl(stream, lut, x, w, bias, y, batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h,
-                         stride_w, pad_top, pad_left, act, flags);
+  return conv2d_fwd_impl(stream, lut, x, w, nullptr, bias, y, batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w,
+                         stride_h, stride_w, pad_top, pad_left, act, flags);
+}
+
+int amsim_conv2d_fwd_scale_bias_act(void* stream, const amsim_lut* lut, const float* x, const float* w,
+                                    const float* scale, const float* bias, float* y, int batch, int in_h, int in_w,
+                                    int in_c, int f_h, int f_w, int out_c, int out_h, int out_w, int stride_h,
+                                    int stride_w, int pad_top, int pad_left, int act, unsigned flags) {
+  return conv2d_fwd_impl(stream, lut, x, w, scale, bias, y, batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w,
+                         stride_h, stride_w, pad_top, pad_left, act, flags);
 }
 
 int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, const float* dy, float* dx, int batch,
@@ -837,37 +896,61 @@ int amsim_dense_bwd_weight(void* stream, const amsim_lut* lut, const float* x, c
   return launch_fgrad((cudaStream_t)stream, p, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
 }
 
-int amsim_matmul(void* stream, const amsim_lut* lut, const float* a, const float* b, float* c, int batch_a,
-                 int batch_b, int row_a, int col_a, int row_b, int col_b, unsigned flags) {
+static int matmul_impl(void* stream, const amsim_lut* lut, const float* a, const float* b, float* c, int batch_a,
+                       int batch_b, int row_a, int col_a, int row_b, int col_b, int trans_a, int trans_b, int has_alpha,
+                       float alpha, unsigned flags) {
   int rc = check_common(lut, flags, true);
   if (rc) return rc;
   if (batch_a < 0 || batch_b < 0 || row_a < 0 || col_a < 0 || row_b < 0 || col_b < 0)
     return fail(AMSIM_ERR_INVALID, "negative matrix dimension");
   if (flags & AMSIM_INT32)
     return fail(AMSIM_ERR_UNSUPPORTED, "MatMulAM is registered for float only (matmulam.cc:269-274)");
-  if (col_a != row_b) return fail(AMSIM_ERR_INVALID, "Does not meet cols of mat a is equal rows of mat b");
+  // logical shapes after the transposes: [M, K] x [K, N]
+  const int M = trans_a ? col_a : row_a, Ka = trans_a ? row_a : col_a;
+  const int Kb = trans_b ? col_b : row_b, N = trans_b ? row_b : col_b;
+  if (Ka != Kb) return fail(AMSIM_ERR_INVALID, "Does not meet cols of mat a is equal rows of mat b");
   if (batch_a > 1 && batch_b > 1 && batch_a != batch_b)
     return fail(AMSIM_ERR_INVALID, "Does not meet batch of mat a is equal batch of matb");
   int nb = batch_a > batch_b ? batch_a : batch_b;
   if (nb == 0) nb = 1;
-  if (row_a == 0 || col_b == 0) return AMSIM_OK;
+  if (M == 0 || N == 0) return AMSIM_OK;
   if (!c) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
-  if (col_a == 0) {  // [x,0] x [0,y]: zeros (matmulam.cc:156-161)
-    CUDA_TRY(cudaMemsetAsync(c, 0, sizeof(float) * (size_t)nb * row_a * col_b, (cudaStream_t)stream));
+  if (Ka == 0) {  // [x,0] x [0,y]: zeros (matmulam.cc:156-161)
+    CUDA_TRY(cudaMemsetAsync(c, 0, sizeof(float) * (size_t)nb * M * N, (cudaStream_t)stream));
     return AMSIM_OK;
   }
   if (!a || !b) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   Params p{};
   p.V = a; p.U = b; p.O = c;
-  p.P = row_a; p.Q = col_b; p.K = col_a;
-  dense_gather(p.g, col_a);
-  p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = col_b; p.u_sq = 1;
-  p.o_sp = col_b; p.o_sq = 1;
+  p.P = M; p.Q = N; p.K = Ka;
+  dense_gather(p.g, Ka);
+  if (trans_a) {
+    // a is stored [K, M]: element (p, k) at a[k * M + p]; the scalar gather path reads it in place
+    p.v_trans = 1;
+    p.v_ld = M;
+  }
+  p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0;
+  if (trans_b) { p.u_sk = 1; p.u_sq = Ka; } else { p.u_sk = N; p.u_sq = 1; }
+  p.o_sp = N; p.o_sq = 1;
   p.v_bs = batch_a > 1 ? (long long)row_a * col_a : 0;
   p.u_bs = batch_b > 1 ? (long long)row_b * col_b : 0;
-  p.o_bs = (long long)row_a * col_b;
+  p.o_bs = (long long)M * N;
+  p.has_alpha = has_alpha;
+  p.alpha = alpha;
   fill_lut(p, lut, true);
   return launch_gather((cudaStream_t)stream, p, nb, flags & AMSIM_DETERMINISTIC, lut->device);
+}
+
+int amsim_matmul(void* stream, const amsim_lut* lut, const float* a, const float* b, float* c, int batch_a,
+                 int batch_b, int row_a, int col_a, int row_b, int col_b, unsigned flags) {
+  return matmul_impl(stream, lut, a, b, c, batch_a, batch_b, row_a, col_a, row_b, col_b, 0, 0, 0, 1.0f, flags);
+}
+
+int amsim_matmul_ex(void* stream, const amsim_lut* lut, const float* a, const float* b, float* c, int batch_a,
+                    int batch_b, int row_a, int col_a, int row_b, int col_b, int transpose_a, int transpose_b,
+                    const float* alpha, unsigned flags) {
+  return matmul_impl(stream, lut, a, b, c, batch_a, batch_b, row_a, col_a, row_b, col_b, transpose_a != 0,
+                     transpose_b != 0, alpha != nullptr, alpha ? *alpha : 1.0f, flags);
 }
 
 }  // extern "C"

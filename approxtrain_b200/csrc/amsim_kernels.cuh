@@ -132,8 +132,15 @@ struct Params {
   int lut_mode;                 // LM_SMEM / LM_GLOBAL / LM_ADD (host-side dispatch)
   int v_first;                  // the lane operand V is the multiplier's first operand (int32 kernels)
   // gather_gemm epilogue: out = act(acc + bias[q]); both optional (exact FP32 add, then max with 0)
+  // out = act(acc * alpha * scale[q] + bias[q]): every factor optional, each step one FP32 operation
   const float* bias;
+  const float* scale;
+  float alpha;                  // used when has_alpha
+  int has_alpha;
   int relu;
+  // gather_gemm, matmul with a transposed first operand: V[p, k] sits at V[k * v_ld + p]
+  int v_trans;
+  long long v_ld;
   // fgrad only
   int k_chunk, splits;
   float* ws;                    // [splits][P][Q] partial sums when splits > 1
@@ -307,9 +314,11 @@ __device__ __forceinline__ void store_out_tile(const Params& prm, float (&acc)[T
     for (int g4 = 0; g4 < TR / 4; ++g4) {
       const int qg = qcol0 + 4 * g4;
       float o[4] = {acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]};
-      if (prm.bias != nullptr || prm.relu) {
+      if (prm.bias != nullptr || prm.relu || prm.scale != nullptr || prm.has_alpha) {
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
+          if (prm.has_alpha) o[r] = __fmul_rn(o[r], prm.alpha);
+          if (prm.scale != nullptr && qg + r < prm.Q) o[r] = __fmul_rn(o[r], __ldg(prm.scale + qg + r));
           if (prm.bias != nullptr && qg + r < prm.Q) o[r] = __fadd_rn(o[r], __ldg(prm.bias + qg + r));
           if (prm.relu) o[r] = o[r] < 0.f ? 0.f : o[r];
         }
@@ -441,7 +450,9 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
           for (int ip = 0; ip < 2; ++ip) {
             float val = 0.f;
             const int u = r0[ip] + kh, v = c0[ip] + kw;
-            if (pv[ip] && kj < prm.K && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
+            if (prm.v_trans) {
+              if (pv[ip] && kj < prm.K) val = __ldg(Vg + (long long)kj * prm.v_ld + (p0 + pl[ip]));
+            } else if (pv[ip] && kj < prm.K && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
               const int row = (int)fdiv((uint32_t)u, g.d_dh), col = (int)fdiv((uint32_t)v, g.d_dw);
               if (row * g.dil_h == u && col * g.dil_w == v)
                 val = __ldg(Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch));
@@ -756,6 +767,129 @@ AMSIM_UNROLL_K
         for (int r = 0; r < 4; ++r)
           if (qg + r < prm.Q) orow[qg + r] = acc[4 * g4 + r][c];
       }
+    }
+  }
+}
+
+// -----------------------------------------------------------------------------
+// fgrad_exact_thin: deterministic filter / weight gradient when the output is small.
+// Every output is one serial FP32 chain over the whole reduction (the reference's order),
+// so the only parallelism is the number of outputs: with 64 chains per thread (fgrad_gemm)
+// a 576 x 64 gradient occupies five CTAs.  Here a thread owns TQ chains (one p, TQ
+// consecutive q), a CTA covers 32 p x 4*TQ q.  grid = (ceil(P/32), ceil(Q/(4*TQ))).
+// -----------------------------------------------------------------------------
+constexpr int THIN_BK = 16;
+
+template <int TQ, int LM>
+__global__ void __launch_bounds__(128) fgrad_exact_thin(const Params prm) {
+  constexpr int NT = 128, BPT = 32, BQT = 4 * TQ;
+  constexpr int BK = THIN_BK;
+  constexpr int NV = BK / 4;                      // V rows staged per thread
+  constexpr int NUQ = (BK * BQT + NT - 1) / NT;   // U elements staged per thread
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);  // [2][BK][32]
+  uint32_t* Us = Vs + 2 * BK * BPT;                  // [2][BK][BQT]
+  const uint32_t smem_base = smem_addr(smem);
+  const uint32_t lut_base = (smem_base + prm.tile_bytes + prm.lut_align - 1) & ~(prm.lut_align - 1);
+  uint8_t* lut_s = smem + (lut_base - smem_base);
+
+  const int t = threadIdx.x, lane = t & 31;
+  const int w = __shfl_sync(0xffffffffu, t >> 5, 0);
+  const int p0 = blockIdx.x * BPT, q0 = blockIdx.y * BQT;
+  const Gather& g = prm.g;
+  const float* __restrict__ Vg = prm.V;
+  const float* __restrict__ Ug = prm.U;
+  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+
+  const uint32_t pg = (uint32_t)(p0 + lane);
+  const bool pv = pg < (uint32_t)prm.P;
+  const uint32_t tap = fdiv(pg, g.d_sc);
+  const int ch = (int)(pg - tap * (uint32_t)g.SC);
+  const int kh = (int)fdiv(tap, g.d_kw);
+  const int kw = (int)tap - kh * g.KW;
+
+  float vraw[NV], uraw[NUQ];
+  auto load_tile = [&](int kb) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int pix = kb * BK + w + 4 * i;
+      float val = 0.f;
+      if (pv && pix < prm.K) {
+        const uint32_t n = fdiv((uint32_t)pix, g.d_img);
+        const uint32_t rem = (uint32_t)pix - n * (uint32_t)(g.PH * g.PW);
+        const uint32_t a = fdiv(rem, g.d_pw);
+        const uint32_t b = rem - a * (uint32_t)g.PW;
+        const int u = (int)a * g.ps_h - g.off_t + kh, v = (int)b * g.ps_w - g.off_l + kw;
+        if ((unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
+          val = __ldg(Vg + (long long)n * ((long long)g.SH * g.SW * g.SC) + ((long long)(u * g.SW + v) * g.SC + ch));
+      }
+      vraw[i] = val;
+    }
+#pragma unroll
+    for (int j = 0; j < NUQ; ++j) {
+      const int e = j * NT + t;
+      const int pix = kb * BK + e / BQT, qg = q0 + e % BQT;
+      uraw[j] = (e < BK * BQT && pix < prm.K && qg < prm.Q)
+                    ? __ldg(Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq) : 0.f;
+    }
+  };
+  auto store_tile = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      Vs[(buf * BK + w + 4 * i) * BPT + lane] = enc_v<true, LM>(__float_as_uint(vraw[i]), prm.m);
+#pragma unroll
+    for (int j = 0; j < NUQ; ++j) {
+      const int e = j * NT + t;
+      if (e < BK * BQT) Us[(buf * BK + e / BQT) * BQT + e % BQT] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
+    }
+  };
+
+  float acc[TQ];
+#pragma unroll
+  for (int r = 0; r < TQ; ++r) acc[r] = 0.f;
+  const int nkb = (prm.K + BK - 1) / BK;
+  if (nkb > 0) {
+    load_tile(0);
+    store_tile(0);
+  }
+  __syncthreads();
+  for (int kb = 0; kb < nkb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < nkb) load_tile(kb + 1);
+    const uint32_t* vs = Vs + buf * BK * BPT + lane;
+    const uint32_t* us = Us + buf * BK * BQT + w * TQ;
+#pragma unroll 16
+    for (int kk = 0; kk < BK; ++kk) {
+      const uint32_t wv = vs[kk * BPT];
+      // same arithmetic as the deterministic branch of mac_step
+      const uint32_t ci = LM == LM_GLOBAL ? (wv & prm.cmask) : ((wv & 0xFFu) | lut_base);
+      const uint32_t cs = (LM == LM_ADD ? wv : (wv & 0xFF800000u)) - 0x3F800000u;
+      const int cn = (int)(0x3F800000u - (wv & 0x7F800000u));
+#pragma unroll
+      for (int r = 0; r < TQ; ++r) {
+        const uint32_t uu = us[kk * BQT + r];
+        const uint32_t pp = uu & 0xFF800000u;
+        const int ee = (int)(uu & 0x7F800000u);
+        uint32_t e;
+        if (LM == LM_ADD) {
+          e = uu & 0x007FFFFFu;
+        } else if (LM == LM_GLOBAL) {
+          const uint32_t v = __ldg(prm.lut_raw + ((uu & prm.rmask) | ci));
+          e = v * prm.mult + (v >> 7) * prm.cadj;
+        } else {
+          e = lds_u8((uu & prm.rmask) | ci) * prm.mult;
+        }
+        if (ee > cn) acc[r] = __fadd_rn(acc[r], __uint_as_float(e + (pp + cs)));
+      }
+    }
+    if (kb + 1 < nkb) store_tile(buf ^ 1);
+    __syncthreads();
+  }
+  if (pv) {
+#pragma unroll
+    for (int r = 0; r < TQ; ++r) {
+      const int qg = q0 + w * TQ + r;
+      if (qg < prm.Q) prm.O[(long long)pg * prm.Q + qg] = acc[r];
     }
   }
 }

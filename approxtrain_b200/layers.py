@@ -111,27 +111,39 @@ class _DenseamBiasActFn(torch.autograd.Function):
 
 
 class _MatMulAMFn(torch.autograd.Function):
+    """C = alpha * op(A) @ op(B).  Gradients follow the four transpose cases of the
+    reference's registered gradient (python/ops/math_ops.py:127-157), every product
+    through MatMulAM with the same LUT; the transposes are index maps in the kernel."""
+
     @staticmethod
-    def forward(ctx, a, b, lut, deterministic):
+    def forward(ctx, a, b, lut, deterministic, ta, tb, alpha):
         ctx.save_for_backward(a, b)
-        ctx.cfg = (lut, deterministic)
-        return ops.matmulam(a, b, mant_mul_lut=lut, deterministic=deterministic)
+        ctx.cfg = (lut, deterministic, ta, tb, alpha)
+        return ops.matmulam(a, b, transpose_a=ta, transpose_b=tb, mant_mul_lut=lut, deterministic=deterministic,
+                            alpha=alpha)
 
     @staticmethod
     def backward(ctx, g):
         a, b = ctx.saved_tensors
-        lut, det = ctx.cfg
+        lut, det, ta, tb, alpha = ctx.cfg
         g = g.contiguous()
+        kw = dict(mant_mul_lut=lut, deterministic=det, alpha=alpha)
         da = db = None
         if ctx.needs_input_grad[0]:
-            da = ops.matmulam(g, b, transpose_b=True, mant_mul_lut=lut, deterministic=det)
+            if not ta:
+                da = ops.matmulam(g, b, transpose_b=not tb, **kw)
+            else:
+                da = ops.matmulam(b, g, transpose_a=tb, transpose_b=True, **kw)
             if a.dim() == 2 and da.dim() == 3:
                 da = da.sum(0)
         if ctx.needs_input_grad[1]:
-            db = ops.matmulam(a, g, transpose_a=True, mant_mul_lut=lut, deterministic=det)
+            if not tb:
+                db = ops.matmulam(a, g, transpose_a=not ta, **kw)
+            else:
+                db = ops.matmulam(g, a, transpose_a=True, transpose_b=ta, **kw)
             if b.dim() == 2 and db.dim() == 3:
                 db = db.sum(0)
-        return da, db, None, None
+        return da, db, None, None, None, None, None
 
 
 def amconv2d(x, w, strides=1, padding="VALID", mant_mul_lut="", deterministic=False):
@@ -147,16 +159,12 @@ def amdense(x, w, mant_mul_lut="", deterministic=False):
     return y.reshape(*lead, w.shape[1])
 
 
-def ammatmul(a, b, mant_mul_lut="", deterministic=False):
-    """Batched AM matmul for rank >= 2 operands with equal leading axes (the op
-    itself takes rank 2/3: matmulam.cc:86-120; extra leading axes are folded
-    into the batch, which is what ammha/multihead_attention.py:18,30 needs)."""
-    if a.dim() > 3:
-        lead = a.shape[:-2]
-        out = _MatMulAMFn.apply(a.reshape(-1, *a.shape[-2:]).contiguous(), b.reshape(-1, *b.shape[-2:]).contiguous(),
-                                mant_mul_lut, deterministic)
-        return out.reshape(*lead, a.shape[-2], b.shape[-1])
-    return _MatMulAMFn.apply(a.contiguous(), b.contiguous(), mant_mul_lut, deterministic)
+def ammatmul(a, b, mant_mul_lut="", deterministic=False, transpose_a=False, transpose_b=False, alpha=None):
+    """Batched AM matmul ``alpha * op(a) @ op(b)`` for rank >= 2 operands with equal
+    leading axes (the reference op takes rank 2/3: matmulam.cc:86-120; extra leading axes
+    are folded into the batch, which is what ammha/multihead_attention.py:18,30 needs)."""
+    return _MatMulAMFn.apply(a.contiguous(), b.contiguous(), mant_mul_lut, deterministic, bool(transpose_a),
+                             bool(transpose_b), alpha)
 
 
 _ACT = {None: lambda t: t, "linear": lambda t: t, "relu": torch.relu, "tanh": torch.tanh,

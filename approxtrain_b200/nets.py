@@ -111,6 +111,7 @@ class _MHA(nn.Module):
         super().__init__()
         kw = dict(mant_mul_lut=lut, deterministic=det)
         self.h, self.d_k, self.lut, self.det = h, d_k, lut, det
+        self.inv_scale = float(torch.tensor(1.0) / torch.tensor(math.sqrt(d_k), dtype=torch.float32))
         self.wq = denseam(d_model, d_k, **kw)
         self.wk = denseam(d_model, d_k, **kw)
         self.wv = denseam(d_model, d_v, **kw)
@@ -123,7 +124,8 @@ class _MHA(nn.Module):
     def forward(self, q, k, v, mask=None):
         q, k, v = self._split(self.wq(q)), self._split(self.wk(k)), self._split(self.wv(v))
         # scores are scaled by sqrt(d_k) with d_k as passed to the layer (multihead_attention.py:16-18)
-        scores = ammatmul(q, k.transpose(-1, -2).contiguous(), self.lut, self.det) / math.sqrt(self.d_k)
+        # (1 / sqrt(d_k) as one FP32 factor in the product's epilogue, K read transposed in place)
+        scores = ammatmul(q, k, self.lut, self.det, transpose_b=True, alpha=self.inv_scale)
         if mask is not None:
             scores = scores + (-1e9) * mask
         o = ammatmul(torch.softmax(scores, -1), v, self.lut, self.det)

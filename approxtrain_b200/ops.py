@@ -206,11 +206,13 @@ def _act_code(activation) -> int:
 
 
 def convam_bias_act(input: torch.Tensor, filter: torch.Tensor, bias, strides=None, padding="VALID",
-                    activation=None, mant_mul_lut: str = "", deterministic: bool = False) -> torch.Tensor:
-    """``act(convam(input, filter) + bias)`` in one launch: the exact bias add and
+                    activation=None, mant_mul_lut: str = "", deterministic: bool = False, scale=None) -> torch.Tensor:
+    """``act(convam(input, filter) * scale + bias)`` in one launch: the exact bias add and
     ReLU that follow the op in the reference's Keras layer
     (am_convolutional.py:267-292) run in the kernel's epilogue, bit-identical to
-    the unfused sequence.  ``bias`` may be None."""
+    the unfused sequence.  ``bias`` may be None.  ``scale`` (per output channel,
+    optional) folds an inference-time BatchNormalization behind the convolution:
+    scale = gamma / sqrt(var + eps), bias = beta - mean * scale."""
     x, w = _prep(input, "input"), _prep(filter, "filter")
     if x.dtype != torch.float32 or w.dtype != torch.float32:
         raise TypeError("the fused epilogue is float32 only")
@@ -223,14 +225,24 @@ def convam_bias_act(input: torch.Tensor, filter: torch.Tensor, bias, strides=Non
         b = _prep(bias, "bias")
         if b.dtype != torch.float32 or tuple(b.shape) != (k,):
             raise ValueError("bias must be float32 of shape [filters]")
+    sc = None
+    if scale is not None:
+        sc = _prep(scale, "scale")
+        if sc.dtype != torch.float32 or tuple(sc.shape) != (k,):
+            raise ValueError("scale must be float32 of shape [filters]")
     sh, sw = _hw(strides, "strides")
     oh, ow, pt, pl = conv2d_geometry(h, wd, kh, kw, sh, sw, padding)
     lut = get_lut(mant_mul_lut, x.device)
     y = torch.empty((n, oh, ow, k), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        check(lib.amsim_conv2d_fwd_bias_act(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(b) if b is not None else None,
-                                            _ptr(y), n, h, wd, c, kh, kw, k, oh, ow, sh, sw, pt, pl,
-                                            _act_code(activation), _flags(deterministic)))
+        if sc is None:
+            check(lib.amsim_conv2d_fwd_bias_act(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(b) if b is not None else None,
+                                                _ptr(y), n, h, wd, c, kh, kw, k, oh, ow, sh, sw, pt, pl,
+                                                _act_code(activation), _flags(deterministic)))
+        else:
+            check(lib.amsim_conv2d_fwd_scale_bias_act(_stream(), lut.handle, _ptr(x), _ptr(w), _ptr(sc),
+                                                      _ptr(b) if b is not None else None, _ptr(y), n, h, wd, c, kh, kw, k,
+                                                      oh, ow, sh, sw, pt, pl, _act_code(activation), _flags(deterministic)))
     return y
 
 
@@ -348,24 +360,34 @@ def denseam_grad(grad: torch.Tensor, input: torch.Tensor, weights: torch.Tensor,
 
 def matmulam(a: torch.Tensor, b: torch.Tensor, transpose_a: bool = False, transpose_b: bool = False,
              adjoint_a: bool = False, adjoint_b: bool = False, a_is_sparse: bool = False, b_is_sparse: bool = False,
-             mant_mul_lut: str = "", deterministic: bool = False) -> torch.Tensor:
-    """Rank 2/3 operands; transposes are materialised before the op like
-    python/ops/math_ops.py:82-93 (the kernel ignores the transpose attrs)."""
+             mant_mul_lut: str = "", deterministic: bool = False, alpha=None) -> torch.Tensor:
+    """``alpha * op(a) @ op(b)`` with the approximate multiplier.  Same arguments as
+    python/ops/math_ops.py:60-93; there the transposes are materialised before the
+    op because its kernel ignores the attrs, here the kernel reads the operands
+    transposed in place.  Operands of rank > 3 (ammha/multihead_attention.py:18
+    passes [batch, heads, seq, d]) have their leading axes folded into the batch;
+    a rank-2 operand or a batch of 1 broadcasts.  ``alpha`` (optional Python float)
+    multiplies every finished sum once in FP32."""
     if adjoint_a or adjoint_b or a_is_sparse or b_is_sparse:
         raise ValueError("Matmulam unsupported args: adjoint_a, adjoint_b, a_is_sparse, b_is_sparse.")
-    if transpose_a:
-        a = a.transpose(-1, -2)
-    if transpose_b:
-        b = b.transpose(-1, -2)
     a, b = _prep(a, "a"), _prep(b, "b")
     if a.dtype != torch.float32 or b.dtype != torch.float32:
         raise TypeError("MatMulAM is registered for float only")
-    if a.dim() not in (2, 3) or b.dim() not in (2, 3):
+    if a.dim() < 2 or b.dim() < 2:
         raise ValueError("Input a and b should be 2 dimensional or 3 dimensional and compitable batch size")
+    lead = None
+    if a.dim() > 3 or b.dim() > 3:
+        if a.dim() != b.dim() or a.shape[:-2] != b.shape[:-2]:
+            raise ValueError("operands of rank > 3 need equal leading axes")
+        lead = tuple(a.shape[:-2])
+        a = a.reshape(-1, *a.shape[-2:])
+        b = b.reshape(-1, *b.shape[-2:])
     ba = a.shape[0] if a.dim() == 3 else 0
     bb = b.shape[0] if b.dim() == 3 else 0
-    m, k = a.shape[-2:]
-    kb, n = b.shape[-2:]
+    ra, ca = a.shape[-2:]
+    rb, cb = b.shape[-2:]
+    m, k = (ca, ra) if transpose_a else (ra, ca)
+    kb, n = (cb, rb) if transpose_b else (rb, cb)
     if ba and bb and not (ba == bb or ba == 1 or bb == 1):
         raise ValueError("Does not meet batch of mat a is equal batch of matb")
     if k != kb:
@@ -373,7 +395,10 @@ def matmulam(a: torch.Tensor, b: torch.Tensor, transpose_a: bool = False, transp
     nb = max(ba, bb)
     lut = get_lut(mant_mul_lut, a.device)
     out = torch.empty((nb, m, n) if nb else (m, n), dtype=torch.float32, device=a.device)
+    al = C.byref(C.c_float(float(alpha))) if alpha is not None else None
     with torch.cuda.device(a.device):
-        check(lib.amsim_matmul(_stream(), lut.handle, _ptr(a), _ptr(b), _ptr(out), ba, bb, m, k, kb, n,
-                               _flags(deterministic)))
+        check(lib.amsim_matmul_ex(_stream(), lut.handle, _ptr(a), _ptr(b), _ptr(out), ba, bb, ra, ca, rb, cb,
+                                  int(bool(transpose_a)), int(bool(transpose_b)), al, _flags(deterministic)))
+    if lead is not None:
+        out = out.reshape(*lead, m, n)
     return out

@@ -139,6 +139,20 @@ int amsim_dense_fwd_bias_act(void* stream, const amsim_lut* lut, const float* x,
                              const float* w, const float* bias, float* y, int batch,
                              int units, int input_width, int act, unsigned flags);
 
+/* The same with a per-output-channel factor first: y = act(conv(x, w) * scale[k] + bias[k]),
+ * one FP32 multiply, one FP32 add, then the activation.  This is an inference-time
+ * BatchNormalization folded behind the convolution (the reference applies Keras
+ * BatchNormalization as a separate exact layer after AMConv2D, e.g.
+ * profile/resnet50_lut.py:568-718): scale = gamma / sqrt(var + eps),
+ * bias = beta - mean * scale.  `scale` and `bias` (out_c floats each) may be NULL.  No
+ * reference counterpart as a fused op; equals the unfused sequence bit for bit. */
+int amsim_conv2d_fwd_scale_bias_act(void* stream, const amsim_lut* lut, const float* x,
+                                    const float* w, const float* scale, const float* bias,
+                                    float* y, int batch, int in_h, int in_w, int in_c,
+                                    int f_h, int f_w, int out_c, int out_h, int out_w,
+                                    int stride_h, int stride_w, int pad_top, int pad_left,
+                                    int act, unsigned flags);
+
 /* Input gradient: replaces ConvamInputGradFunctor<GPUDevice> (convam.h:82-93,
  * cuda/cuda_kernel.cu:462-657) including cuda/reverseNswapdim23.cu.  The
  * functor's hole_grad_* and back-pad arguments are derived here from the
@@ -224,6 +238,24 @@ int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w,
 int amsim_matmul(void* stream, const amsim_lut* lut, const float* a,
                  const float* b, float* c, int batch_a, int batch_b, int row_a,
                  int col_a, int row_b, int col_b, unsigned flags);
+
+/* MatMulAM with the transposes done by the kernel's index maps and an optional scalar
+ * factor.  The reference op declares transpose_a / transpose_b but its kernel ignores them
+ * (matmulam.cc:48-56, cuda/matmulam_kernel.cu:11-99), so its Python wrapper materialises the
+ * transposed operand first (python/ops/math_ops.py:82-93); here row_* / col_* describe the
+ * operands AS STORED and transpose_* says to read them transposed in place:
+ *   C = alpha * op(A) x op(B),  op(X) = X^T when transpose_x != 0.
+ * Products are AM(op(A)[i,k], op(B)[k,j]) summed over ascending k as in amsim_matmul.
+ * `alpha` (host pointer, may be NULL) multiplies every finished sum once in FP32: the
+ * 1/sqrt(d_k) of scaled dot-product attention (ammha/multihead_attention.py:18-30). */
+int amsim_matmul_ex(void* stream, const amsim_lut* lut, const float* a, const float* b,
+                    float* c, int batch_a, int batch_b, int row_a, int col_a, int row_b,
+                    int col_b, int transpose_a, int transpose_b, const float* alpha,
+                    unsigned flags);
+
+/* Number of kernels this library has launched since it was loaded (all devices, all
+ * streams).  For benchmarks that report their launch count; no reference counterpart. */
+unsigned long long amsim_debug_launch_count(void);
 
 /* Host-side check of the kernels' constant-divisor arithmetic (no GPU work):
  * returns n / d computed the way the device code does.  For tests. */

@@ -93,6 +93,36 @@ def test_matmul_gradient_wiring(oracle, luts):
     assert beq(b.grad.cpu().numpy().reshape(6, 5, 7), oracle.matmul(np.ascontiguousarray(an.transpose(0, 2, 1)), gn, lut, m))
 
 
+@pytest.mark.parametrize("ta,tb", [(False, True), (True, False), (True, True)])
+def test_matmul_gradient_wiring_with_transposes_and_alpha(oracle, luts, ta, tb):
+    """The four transpose cases of the reference's MatMulAM gradient (math_ops.py:127-157),
+    alpha applied to both gradients."""
+    from approxtrain_b200.layers import ammatmul
+    lut, m = luts["MIT_7"]
+    rng = np.random.default_rng(16)
+    M, K, N, al = 8, 5, 7, 0.25
+    an = rng.standard_normal((6, K, M) if ta else (6, M, K)).astype(np.float32)
+    bn = rng.standard_normal((6, N, K) if tb else (6, K, N)).astype(np.float32)
+    a = torch.from_numpy(an).cuda().requires_grad_()
+    b = torch.from_numpy(bn).cuda().requires_grad_()
+    c = ammatmul(a, b, lut_path("MIT_7"), True, transpose_a=ta, transpose_b=tb, alpha=al)
+    gn = rng.standard_normal((6, M, N)).astype(np.float32)
+    c.backward(torch.from_numpy(gn).cuda())
+    T = lambda x: np.ascontiguousarray(x.transpose(0, 2, 1))
+    opa, opb = (T(an) if ta else an), (T(bn) if tb else bn)
+    assert beq(c.detach().cpu().numpy(), oracle.matmul(opa, opb, lut, m) * np.float32(al))
+    if not ta:
+        want_da = oracle.matmul(gn, T(opb), lut, m)
+    else:
+        want_da = oracle.matmul(opb, T(gn), lut, m)
+    if not tb:
+        want_db = oracle.matmul(T(opa), gn, lut, m)
+    else:
+        want_db = oracle.matmul(T(gn), opa, lut, m)
+    assert beq(a.grad.cpu().numpy(), want_da * np.float32(al))
+    assert beq(b.grad.cpu().numpy(), want_db * np.float32(al))
+
+
 def test_lenet5_trains_on_a_fixed_batch():
     """BASELINE config 2 shapes: batch 128 of 28x28x1, MIT_7, He-normal."""
     from approxtrain_b200.nets import LeNet5

@@ -293,8 +293,41 @@ def test_matmul_transpose_flags_and_errors(ops, oracle, luts):
         ops.matmulam(dev(q), dev(k), mant_mul_lut=lut_path("MIT_7"))
     with pytest.raises(ValueError, match="batch of mat a"):
         ops.matmulam(dev(q), dev(np.zeros((2, 8, 5), np.float32)), mant_mul_lut=lut_path("MIT_7"))
-    with pytest.raises(ValueError, match="2 dimensional or 3 dimensional"):
+    with pytest.raises(ValueError, match="equal leading axes"):
         ops.matmulam(dev(np.zeros((2, 2, 2, 2), np.float32)), dev(np.zeros((2, 2), np.float32)), mant_mul_lut=lut_path("MIT_7"))
+    with pytest.raises(ValueError, match="2 dimensional or 3 dimensional"):
+        ops.matmulam(dev(np.zeros((2,), np.float32)), dev(np.zeros((2, 2), np.float32)), mant_mul_lut=lut_path("MIT_7"))
+
+
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+def test_matmul_transposes_in_the_kernel_and_alpha(ops, oracle, luts, ta, tb):
+    """transpose_a / transpose_b are index maps in the kernel (the reference materialises
+    them in Python, math_ops.py:82-93): deterministic results are bit-identical to the
+    oracle on the materialised operands, for batched, broadcast and rank-4 operands; alpha
+    is one FP32 multiply of the finished sum."""
+    lut, m = luts["MBM_7"]
+    p7 = lut_path("MBM_7")
+    rng = np.random.default_rng(12)
+    M, K, N = 37, 70, 45
+    def mk(batch, r, c, t):
+        shp = (c, r) if t else (r, c)
+        return rng.standard_normal(batch + shp).astype(np.float32)
+    def mat(x, t):
+        return np.ascontiguousarray(np.swapaxes(x, -1, -2)) if t else x
+    for ba, bb in [((), ()), ((4,), (4,)), ((4,), ()), ((1,), (3,)), ((2, 3), (2, 3))]:
+        a, b = mk(ba, M, K, ta), mk(bb, K, N, tb)
+        want = oracle.matmul(mat(a, ta).reshape((-1, M, K)) if len(ba) == 2 else mat(a, ta),
+                             mat(b, tb).reshape((-1, K, N)) if len(bb) == 2 else mat(b, tb), lut, m)
+        got = ops.matmulam(dev(a), dev(b), transpose_a=ta, transpose_b=tb, mant_mul_lut=p7, deterministic=True)
+        assert_bit_equal(got.cpu().numpy().reshape(want.shape), want, f"det ta={ta} tb={tb} {ba} {bb}")
+        fast = ops.matmulam(dev(a), dev(b), transpose_a=ta, transpose_b=tb, mant_mul_lut=p7)
+        assert_close(fast.cpu().numpy().reshape(want.shape), want, f"fast ta={ta} tb={tb} {ba} {bb}")
+        for det in (True, False):
+            base = ops.matmulam(dev(a), dev(b), transpose_a=ta, transpose_b=tb, mant_mul_lut=p7, deterministic=det)
+            al = float(np.float32(1.0) / np.float32(np.sqrt(70.0)))
+            sc = ops.matmulam(dev(a), dev(b), transpose_a=ta, transpose_b=tb, mant_mul_lut=p7, deterministic=det, alpha=al)
+            assert torch.equal(sc, base * al), "alpha is one FP32 multiply"
 
 
 def test_empty_and_degenerate_inputs(ops):
@@ -428,6 +461,38 @@ def test_balanced_launch_of_the_reduction(ops, oracle, luts, balanced, monkeypat
     # deterministic mode never splits a reduction
     yd = ops.convam(dev(x), dev(wt), strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=p7, deterministic=True).cpu().numpy()
     assert_bit_equal(yd, oracle.conv2d_fwd(g, x, wt, lut, m), "deterministic mode ignores the balanced launch")
+
+
+@pytest.mark.parametrize("thin", [None, "1", "0"])
+def test_deterministic_filter_gradient_thin_and_tiled_kernels(ops, oracle, luts, thin, monkeypatch, tmp_path):
+    """Deterministic filter / weight gradients keep one serial chain per output; small
+    outputs run with few chains per thread (whole device busy), large ones with the
+    64-chain register tile.  Both kernels, forced and as chosen by the library, are
+    bit-identical to the oracle for every table mode."""
+    if thin is not None:
+        monkeypatch.setenv("AMSIM_THIN_FGRAD", thin)
+    rng = np.random.default_rng(91)
+    lut9 = rng.integers(0, 256, size=1 << 18, dtype=np.uint8)
+    path9 = str(tmp_path / "RAND_9.bin")
+    lut9.tofile(path9)
+    tables = [(lut_path("MBM_7"),) + luts["MBM_7"], (lut_path("MIT_7"),) + luts["MIT_7"], (lut_path("MBM_3"),) + luts["MBM_3"],
+              (path9, lut9, 9)]
+    cases = [(2, 9, 9, 8, 3, 3, 20, 1, "SAME"), (3, 12, 12, 3, 5, 5, 6, 2, "VALID"), (2, 10, 10, 64, 1, 1, 130, 1, "VALID"),
+             (1, 16, 16, 32, 3, 3, 40, 2, "SAME")]
+    for (path, lut, m) in tables:
+        for (n, h, w, c, kh, kw, k, s, pad) in cases:
+            x, _ = _conv_case(rng, n, h, w, c, kh, kw, k)
+            g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+            dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+            dw = ops.convam_filter_grad((kh, kw, c, k), dev(x), dev(dy), strides=[1, s, s, 1], padding=pad,
+                                        mant_mul_lut=path, deterministic=True).cpu().numpy()
+            assert_bit_equal(dw, oracle.conv2d_bwd_filter(g, x, dy, lut, m), f"det filter-grad thin={thin} {path[-9:]}")
+        xd = rng.standard_normal((37, 50)).astype(np.float32)
+        xd[xd < -0.5] = 0
+        wd = rng.standard_normal((50, 70)).astype(np.float32)
+        gd = rng.standard_normal((37, 70)).astype(np.float32)
+        _, dwd = ops.denseam_grad(dev(gd), dev(xd), dev(wd), path, deterministic=True)
+        assert_bit_equal(dwd.cpu().numpy(), oracle.dense_bwd_weight(xd, gd, lut, m), f"det dense weight-grad thin={thin}")
 
 
 @pytest.mark.parametrize("m", [8, 9, 11])
@@ -575,6 +640,16 @@ def test_fused_bias_relu_epilogue_equals_unfused_sequence(ops, oracle, luts):
         got = ops.convam_bias_act(dev(x), dev(wt), dev(b), strides=[1, s, s, 1], padding=pad, activation="relu",
                                   mant_mul_lut=p, deterministic=True).cpu().numpy()
         assert np.array_equal(got, ref)
+    # per-channel scale before the bias: an inference BatchNormalization folded behind the convolution
+    x, wt = _conv_case(rng, 2, 9, 9, 8, 3, 3, 20)
+    sc = (rng.standard_normal(20) * 0.5 + 1).astype(np.float32)
+    b = rng.standard_normal(20).astype(np.float32)
+    for det in (True, False):
+        kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=p, deterministic=det)
+        base = ops.convam(dev(x), dev(wt), **kw_)
+        got = ops.convam_bias_act(dev(x), dev(wt), dev(b), activation="relu", scale=dev(sc), **kw_)
+        assert torch.equal(got, torch.relu(base * dev(sc) + dev(b))), det
+        assert torch.equal(ops.convam_bias_act(dev(x), dev(wt), None, scale=dev(sc), **kw_), base * dev(sc))
     xd = rng.standard_normal((33, 50)).astype(np.float32)
     wd = rng.standard_normal((50, 70)).astype(np.float32)
     bd = rng.standard_normal(70).astype(np.float32)
