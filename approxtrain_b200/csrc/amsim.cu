@@ -62,6 +62,7 @@ struct amsim_lut {
   uint8_t* d_trans = nullptr;  // encoded, row = second operand (b)  [m <= 7]
   int enc_bytes = 0;           // size of each encoded copy, multiple of 16
   bool additive = false;       // encoded entry(i, j) == i + j for every pair: no lookups needed
+  int direct = 0;              // LM_DIRECT_MBM / LM_DIRECT_MIT: no table at all, m = 23
 };
 
 namespace {
@@ -185,7 +186,7 @@ void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
   p.rmask = ((1u << lut->m) - 1u) << lut->m;
   p.cmask = (1u << lut->m) - 1u;
   p.cadj = (1u << 23) - 128u * p.mult;
-  p.lut_mode = lut->m > 7 ? LM_GLOBAL : (lut->additive ? LM_ADD : LM_SMEM);
+  p.lut_mode = lut->direct ? lut->direct : lut->m > 7 ? LM_GLOBAL : (lut->additive ? LM_ADD : LM_SMEM);
   p.lut_raw = v_is_first_operand ? lut->d_raw_t : lut->d_raw;
   p.v_first = v_is_first_operand ? 1 : 0;
   uint32_t al = 16;
@@ -346,6 +347,9 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
     if (exact) { if (vec) AMSIM_GO(true, true, LM_); else AMSIM_GO(true, false, LM_); }         \
     else       { if (vec) AMSIM_GO(false, true, LM_); else AMSIM_GO(false, false, LM_); }       \
   } while (0)
+  // direct models: per-product arithmetic dominates; one kernel flavour (ordered chains) serves both modes
+  if (p.lut_mode == LM_DIRECT_MBM) { if (vec) AMSIM_GO(true, true, LM_DIRECT_MBM); else AMSIM_GO(true, false, LM_DIRECT_MBM); }
+  if (p.lut_mode == LM_DIRECT_MIT) { if (vec) AMSIM_GO(true, true, LM_DIRECT_MIT); else AMSIM_GO(true, false, LM_DIRECT_MIT); }
   if (p.lut_mode == LM_ADD) AMSIM_GO_LM(LM_ADD);
   if (p.lut_mode == LM_GLOBAL) AMSIM_GO_LM(LM_GLOBAL);
   AMSIM_GO_LM(LM_SMEM);
@@ -421,6 +425,7 @@ int launch_fgrad_thin(cudaStream_t st, Params& p, int tq, int device) {
 
 int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_bytes, int device) {
   if (p.P <= 0 || p.Q <= 0) return AMSIM_OK;
+  if (lm_direct(p.lut_mode)) exact = true;  // one kernel flavour for the direct models: ordered chains
   const FgradPlan f = plan_fgrad(p.P, p.Q, p.K, exact);
   if (f.ws_bytes > 0) {
     if (!ws || ws_bytes < f.ws_bytes)
@@ -440,6 +445,8 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
     if (thin) {
       int tq = chains >= 4ll * 32 * 4 * 148 * 2 ? 4 : chains >= 2ll * 32 * 4 * 148 * 2 ? 2 : 1;
       if (const char* e = getenv("AMSIM_THIN_TQ")) tq = atoi(e);
+      if (p.lut_mode == LM_DIRECT_MBM) return launch_fgrad_thin<LM_DIRECT_MBM>(st, p, tq, device);
+      if (p.lut_mode == LM_DIRECT_MIT) return launch_fgrad_thin<LM_DIRECT_MIT>(st, p, tq, device);
       if (p.lut_mode == LM_ADD) return launch_fgrad_thin<LM_ADD>(st, p, tq, device);
       if (p.lut_mode == LM_GLOBAL) return launch_fgrad_thin<LM_GLOBAL>(st, p, tq, device);
       return launch_fgrad_thin<LM_SMEM>(st, p, tq, device);
@@ -452,6 +459,8 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
     if (exact) { if (vec) AMSIM_GO(true, true, LM_); else AMSIM_GO(true, false, LM_); }         \
     else       { if (vec) AMSIM_GO(false, true, LM_); else AMSIM_GO(false, false, LM_); }       \
   } while (0)
+  if (p.lut_mode == LM_DIRECT_MBM) { if (vec) AMSIM_GO(true, true, LM_DIRECT_MBM); else AMSIM_GO(true, false, LM_DIRECT_MBM); }
+  if (p.lut_mode == LM_DIRECT_MIT) { if (vec) AMSIM_GO(true, true, LM_DIRECT_MIT); else AMSIM_GO(true, false, LM_DIRECT_MIT); }
   if (p.lut_mode == LM_ADD) AMSIM_GO_LM(LM_ADD);
   if (p.lut_mode == LM_GLOBAL) AMSIM_GO_LM(LM_GLOBAL);
   AMSIM_GO_LM(LM_SMEM);
@@ -462,6 +471,7 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
 // T = int32: one thread per output on the raw table (see naive_*_i32).
 int launch_naive_i32(cudaStream_t st, Params& p, const amsim_lut* lut, bool fgrad) {
   if (p.P <= 0 || p.Q <= 0) return AMSIM_OK;
+  if (lut->direct) return fail(AMSIM_ERR_UNSUPPORTED, "the direct 32-bit models are FP32 only");
   p.lut_raw = lut->d_raw;  // rows by the first operand; v_first tells the kernel which operand that is
   const long long n = (long long)p.P * p.Q;
   const unsigned blocks = (unsigned)((n + 127) / 128);
@@ -507,6 +517,33 @@ int amsim_lut_open_bytes(const uint8_t* bytes, int m, int device, amsim_lut** ou
 int amsim_lut_open(const char* path, int device, amsim_lut** out) {
   if (!path || !out) return fail(AMSIM_ERR_INVALID, "NULL argument");
   if (!*path) return fail(AMSIM_ERR_LUT_NAME, "no mant lut file name given");
+  if (strncmp(path, "direct:", 7) == 0) {
+    // mantissa width 23: the reference's direct C simulation instead of a table (README.md:107)
+    int kind = 0;
+    if (strcmp(path + 7, "MBM32") == 0) kind = LM_DIRECT_MBM;
+    else if (strcmp(path + 7, "MIT32") == 0) kind = LM_DIRECT_MIT;
+    else return fail(AMSIM_ERR_LUT_NAME, "unknown direct multiplier '%s' (direct:MBM32, direct:MIT32)", path + 7);
+    const std::string key = std::string(path) + "@" + std::to_string(device);
+    std::lock_guard<std::mutex> lk(g_lut_mu);
+    auto it = g_lut_cache.find(key);
+    if (it != g_lut_cache.end()) {
+      it->second->refs++;
+      *out = it->second;
+      return AMSIM_OK;
+    }
+    int ndev = 0;
+    CUDA_TRY(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return fail(AMSIM_ERR_INVALID, "device %d out of range", device);
+    amsim_lut* h = new amsim_lut();
+    h->m = 23;
+    h->device = device;
+    h->refs = 1;
+    h->direct = kind;
+    h->key = key;
+    g_lut_cache[key] = h;
+    *out = h;
+    return AMSIM_OK;
+  }
   const int m = parse_mant_width(path);
   if (m < 0) return fail(AMSIM_ERR_LUT_NAME, "cannot take a mantissa width in 1..11 from '%s' (expected <MODEL>_<m>.bin)", path);
   char real[PATH_MAX];
@@ -559,7 +596,7 @@ int amsim_lut_info(const amsim_lut* lut, int* mant_width, uint32_t* mant_mask, i
   if (!lut) return fail(AMSIM_ERR_INVALID, "lut handle is NULL");
   if (mant_width) *mant_width = lut->m;
   if (mant_mask) *mant_mask = ((1u << lut->m) - 1u) << (23 - lut->m);  // approx_mul_lut.h:28
-  if (a_shift) *a_shift = 23 - 2 * lut->m;                             // :26
+  if (a_shift) *a_shift = lut->direct ? 0 : 23 - 2 * lut->m;           // :26
   if (b_shift) *b_shift = 23 - lut->m;                                 // :27
   if (device_bytes) *device_bytes = lut->d_raw;
   return AMSIM_OK;
@@ -573,7 +610,7 @@ int amsim_mul(void* stream, const amsim_lut* lut, const float* a, const float* b
   size_t blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   AMSIM_COUNT_LAUNCH();
-  mul_elementwise<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, lut->d_raw, lut->m);
+  mul_elementwise<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, lut->d_raw, lut->m, lut->direct);
   CUDA_TRY(cudaGetLastError());
   return AMSIM_OK;
 }

@@ -174,6 +174,40 @@ constexpr int LM_ADD = 2;     // additive table, entry(i, j) == i + j for every 
                               // multipliers): the lookup is an integer add of the operands' mantissa
                               // fields, no table access at all; detected when the LUT is opened
 
+constexpr int LM_DIRECT_MBM = 3;  // no table: the 32-bit minimally-biased model computed per product
+constexpr int LM_DIRECT_MIT = 4;  // no table: the 32-bit Mitchell model computed per product
+__host__ __device__ constexpr bool lm_direct(int lm) { return lm == LM_DIRECT_MBM || lm == LM_DIRECT_MIT; }
+
+// Direct simulation of the reference's 32-bit multipliers (cuda/FPmultMBM_fast32.inl:13-126,
+// cuda/Mitchell_32.inl), for mantissa widths too large for a table.  Sign and exponent come
+// from the exact FP32 product; the mantissa is the approximate one; the exponent moves by
+// ("approximate mantissa product reached 2") - ("exact mantissa product, rounded to 24 bits,
+// reached 2").  An exact product that is inf/NaN passes through, one that is zero or
+// subnormal gives +0.  The rounded exact mantissa product is taken from an FP32 multiply of
+// 1.ma and 1.mb (same round-to-nearest-even at the same bit as the reference's 48-bit
+// integer product with hand rounding).
+template <bool MBM>
+__device__ __forceinline__ uint32_t direct_mul_bits(uint32_t at, uint32_t bt) {
+  const uint32_t eb = __float_as_uint(__fmul_rn(__uint_as_float(at), __uint_as_float(bt)));
+  const uint32_t eexp = (eb >> 23) & 0xFFu;
+  if (eexp == 255u) return eb;
+  if (eexp == 0u) return 0u;
+  const uint32_t ma = at & 0x7FFFFFu, mb = bt & 0x7FFFFFu;
+  const uint32_t exact_two =
+      __fmul_rn(__uint_as_float(0x3F800000u | ma), __uint_as_float(0x3F800000u | mb)) >= 2.0f ? 1u : 0u;
+  const uint32_t s = ma + mb;
+  const uint32_t carry = s >> 23;  // s < 2^24
+  uint32_t t = s & 0x7FFFFFu;
+  if (MBM) {
+    t += 0xA0000u >> carry;                    // 2^-4 + 2^-6, halved after a carry
+    if (carry && t >= 0x800000u) t = s;        // correction would overflow: dropped
+  }
+  uint32_t w = (0x800000u + t) << carry;
+  const uint32_t approx_two = w >= 0x1000000u ? 1u : 0u;
+  w >>= approx_two;
+  return (eb & 0x80000000u) + ((eexp - exact_two + approx_two) << 23) + (w & 0x7FFFFFu);
+}
+
 // ---- operand encodings -------------------------------------------------------
 // Lane operand (V): one word = sign+exponent bits | table column.
 //   fast:  a zero exponent field (zero or denormal) becomes the word 0, which
@@ -184,6 +218,7 @@ constexpr int LM_ADD = 2;     // additive table, entry(i, j) == i + j for every 
 //          a column index (sign | exponent | truncated mantissa).
 template <bool EXACT, int LM>
 __device__ __forceinline__ uint32_t enc_v(uint32_t bits, int m) {
+  if (lm_direct(LM)) return bits;  // the model works on the raw operands
   uint32_t w;
   if (LM == LM_ADD) {
     w = bits & ~((1u << (23 - m)) - 1u);
@@ -235,6 +270,10 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
       const uint32_t du = uu[r] & 0x007FFFFFu;  // additive table: the uniform operand's mantissa field
 #pragma unroll
       for (int t = 0; t < TC; ++t) {
+        if (lm_direct(LM)) {  // both models are symmetric in their operands
+          acc[4 * g4 + r][t] = __fadd_rn(acc[4 * g4 + r][t], __uint_as_float(direct_mul_bits<LM == LM_DIRECT_MBM>(w[t], uu[r])));
+          continue;
+        }
         // e = (carry << 23) + (mantissa bits << (23 - m)), AMsimulator.inl:22-23,31
         uint32_t e;
         if (LM == LM_ADD) {
@@ -271,6 +310,7 @@ __device__ __forceinline__ void copy_lut_to_smem(uint8_t* lut_s, const uint8_t* 
 // Uniform operand (U): one word = sign+exponent bits | table row bits.
 template <int LM>
 __device__ __forceinline__ uint32_t enc_u(uint32_t bits, int m) {
+  if (lm_direct(LM)) return bits;
   if (LM == LM_ADD) return bits & ~((1u << (23 - m)) - 1u);  // sign | exponent | truncated mantissa
   return (bits & 0xFF800000u) | (((bits >> (23 - m)) & ((1u << m) - 1u)) << m);
 }
@@ -868,6 +908,10 @@ __global__ void __launch_bounds__(128) fgrad_exact_thin(const Params prm) {
 #pragma unroll
       for (int r = 0; r < TQ; ++r) {
         const uint32_t uu = us[kk * BQT + r];
+        if (lm_direct(LM)) {
+          acc[r] = __fadd_rn(acc[r], __uint_as_float(direct_mul_bits<LM == LM_DIRECT_MBM>(wv, uu)));
+          continue;
+        }
         const uint32_t pp = uu & 0xFF800000u;
         const int ee = (int)(uu & 0x7F800000u);
         uint32_t e;
@@ -984,9 +1028,15 @@ __global__ void naive_fgrad_i32(const Params prm) {
 }
 
 __global__ void mul_elementwise(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
-                                size_t n, const uint8_t* __restrict__ lut, int m) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    out[i] = __uint_as_float(am_mul_bits(__float_as_uint(a[i]), __float_as_uint(b[i]), lut, m));
+                                size_t n, const uint8_t* __restrict__ lut, int m, int lut_mode) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const uint32_t at = __float_as_uint(a[i]), bt = __float_as_uint(b[i]);
+    uint32_t r;
+    if (lut_mode == LM_DIRECT_MBM) r = direct_mul_bits<true>(at, bt);
+    else if (lut_mode == LM_DIRECT_MIT) r = direct_mul_bits<false>(at, bt);
+    else r = am_mul_bits(at, bt, lut, m);
+    out[i] = __uint_as_float(r);
+  }
 }
 
 }  // namespace amsim

@@ -86,7 +86,17 @@ const char* amsim_version(void);
  * A table whose entries satisfy (carry << m) + mantissa == i + j for every
  * index pair (Mitchell's logarithmic multiplier, e.g. MIT_7) needs no lookups:
  * the kernels add the operands' mantissa fields instead, with identical bits
- * (set AMSIM_NO_ADDITIVE in the environment before opening to force the table). */
+ * (set AMSIM_NO_ADDITIVE in the environment before opening to force the table).
+ *
+ * Two pseudo-paths select the reference's direct C simulation of its 32-bit
+ * multipliers (mantissa width 23, README.md:107: "for multipliers with mantissa
+ * bit-width greater or equal to 12, direct C simulation should be used"):
+ *   "direct:MBM32"  cuda/FPmultMBM_fast32.inl:41-126 (FMBM32_MULTIPLIER)
+ *   "direct:MIT32"  cuda/Mitchell_32.inl (MITCHEL23_MULTIPLIER)
+ * No file is read; every product is computed arithmetically inside the same GEMM
+ * kernels (sign/exponent of the exact FP32 product, approximate mantissa, inf/NaN
+ * passed through, zero/subnormal products flushed to +0).  Both accumulate in the
+ * reference's order whatever the mode flag says; FP32 only. */
 int amsim_lut_open(const char* path, int device, amsim_lut** out);
 /* Same, from bytes already in host memory (m given explicitly). */
 int amsim_lut_open_bytes(const uint8_t* bytes, int m, int device, amsim_lut** out);

@@ -77,9 +77,50 @@ int am_load_lut(const char* path, uint8_t** out, int* m_out) {
   return 0;
 }
 
+/* Direct simulation of the 32-bit multipliers (mantissa width 23: too wide for a
+ * table), the reference's cuda/FPmultMBM_fast32.inl:13-126 and cuda/Mitchell_32.inl.
+ * Both take sign and exponent from the exact FP32 product, replace its mantissa by
+ * an approximate one and move the exponent by the difference between "the exact
+ * mantissa product reached 2" and "the approximate one reached 2"; an exact product
+ * that is inf/NaN is passed through, one that is zero or subnormal gives +0.
+ *
+ * Restated arithmetic (not the reference's statement order):
+ *  - "the exact mantissa product, rounded to 24 bits, reached 2"
+ *    (FPmultMBM_fast32.inl:71-92: a 48-bit integer product, then round-to-nearest-
+ *    even by hand) is the FP32 product of 1.ma and 1.mb compared with 2: the
+ *    hardware rounding is the same round-to-nearest-even at the same bit;
+ *  - MBM mantissa (:13-36): s = ma + mb; carry = s >= 2^23; t = (s mod 2^23) +
+ *    (0xA0000 >> carry); if carry and t >= 2^23 the correction is dropped (t = s);
+ *    w = (2^23 + t) << carry; Mitchell (Mitchell_32.inl:13-32): t = s mod 2^23;
+ *  - approximate "reached 2": w >= 2^24, then w >>= 1; mantissa = w mod 2^23. */
+static uint32_t direct_mul_bits(uint32_t at, uint32_t bt, int mbm) {
+  const float exact = u2f(at) * u2f(bt);
+  const uint32_t eb = f2u(exact);
+  const uint32_t eexp = (eb >> 23) & 0xffu;
+  if (eexp == 255u) return eb;
+  if (eexp == 0u) return 0u;
+  const uint32_t ma = at & 0x7fffffu, mb = bt & 0x7fffffu;
+  const int exact_two = u2f(0x3f800000u | ma) * u2f(0x3f800000u | mb) >= 2.0f;
+  const uint32_t s = ma + mb;
+  const uint32_t carry = s >= 0x800000u;
+  uint32_t t = s & 0x7fffffu;
+  if (mbm) {
+    t += 0xA0000u >> carry;
+    if (carry && t >= 0x800000u) t = s;
+  }
+  uint32_t w = (0x800000u + t) << carry;
+  const int approx_two = w >= 0x1000000u;
+  if (approx_two) w >>= 1;
+  const uint32_t e = eexp - (uint32_t)exact_two + (uint32_t)approx_two;
+  return (eb & 0x80000000u) + (e << 23) + (w & 0x7fffffu);
+}
+
 /* cuda/AMsimulator.inl:13-36.  mant_mask / a_shift / b_shift as derived in
- * approx_mul_lut.h:26-28. */
+ * approx_mul_lut.h:26-28.  The pseudo-widths AM_DIRECT_MBM32 / AM_DIRECT_MIT32
+ * select the direct 32-bit models instead (lut is ignored). */
 uint32_t am_mul_bits(uint32_t at, uint32_t bt, const uint8_t* lut, int m) {
+  if (m == AM_DIRECT_MBM32) return direct_mul_bits(at, bt, 1);
+  if (m == AM_DIRECT_MIT32) return direct_mul_bits(at, bt, 0);
   const uint32_t mant_mask = ((1u << m) - 1u) << (23 - m);
   const uint32_t a_shift = (uint32_t)(23 - 2 * m);
   const uint32_t b_shift = (uint32_t)(23 - m);

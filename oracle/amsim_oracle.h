@@ -38,6 +38,12 @@ int am_parse_mant_width(const char* path);
  * 2^(2m) bytes.  Returns 0 on success; *out is malloc'ed, caller frees. */
 int am_load_lut(const char* path, uint8_t** out, int* m);
 
+/* Pseudo mantissa widths: every function below that takes (lut, m) runs the
+ * reference's direct 32-bit model instead of a table when m is one of these
+ * (cuda/FPmultMBM_fast32.inl:41-126, cuda/Mitchell_32.inl; lut may be NULL). */
+#define AM_DIRECT_MBM32 132
+#define AM_DIRECT_MIT32 123
+
 /* cuda/AMsimulator.inl:13-36 on raw bit patterns. */
 uint32_t am_mul_bits(uint32_t at, uint32_t bt, const uint8_t* lut, int m);
 float am_mul(float a, float b, const uint8_t* lut, int m);

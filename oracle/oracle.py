@@ -20,6 +20,11 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_HERE, "libamsim_oracle.so")
 _REF_LIB = os.path.join(_HERE, "_ref", "libref_amsim.so")
 
+# Pseudo mantissa widths selecting the direct 32-bit models (amsim_oracle.h); pass NO_LUT as the table.
+DIRECT_MBM32 = 132
+DIRECT_MIT32 = 123
+NO_LUT = np.zeros(1, dtype=np.uint8)
+
 _f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 _u32p = np.ctypeslib.ndpointer(dtype=np.uint32, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
@@ -260,6 +265,16 @@ class RefPrimitive:
         bt = np.ascontiguousarray(bt, np.uint32).reshape(-1)
         out = np.empty_like(at)
         self.lib.ref_am_mul_bits_array(at, bt, out, at.size, lut, m)
+        return out
+
+    def direct_mul_bits_array(self, at: np.ndarray, bt: np.ndarray, m: int) -> np.ndarray:
+        """The reference's cuda/FPmultMBM_fast32.inl (m = DIRECT_MBM32) or
+        cuda/Mitchell_32.inl (m = DIRECT_MIT32) on raw bit patterns."""
+        at = np.ascontiguousarray(at, np.uint32).reshape(-1)
+        bt = np.ascontiguousarray(bt, np.uint32).reshape(-1)
+        out = np.empty_like(at)
+        self.lib.ref_direct_mul_bits_array.argtypes = [_u32p, _u32p, _u32p, C.c_uint64, C.c_int]
+        self.lib.ref_direct_mul_bits_array(at, bt, out, at.size, 1 if m == DIRECT_MBM32 else 0)
         return out
 
 

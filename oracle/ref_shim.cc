@@ -36,3 +36,28 @@ extern "C" void ref_am_mul_bits_array(const uint32_t* at, const uint32_t* bt, ui
                                       uint64_t n, const uint8_t* lut, int m) {
   for (uint64_t i = 0; i < n; ++i) out[i] = ref_am_mul_bits(at[i], bt[i], lut, m);
 }
+
+// The reference's direct 32-bit models (cuda/FPmultMBM_fast32.inl:41-126,
+// cuda/Mitchell_32.inl), device functions compiled as host C++.  Both files define the
+// same four mask macros with the same values.
+#undef MANTISSA_MASK
+#undef EXPONENT_MASK
+#undef MANTISSA_MASK_INV
+#undef SIGN_MASK
+#include "FPmultMBM_fast32.inl"
+#undef MANTISSA_MASK
+#undef EXPONENT_MASK
+#undef MANTISSA_MASK_INV
+#undef SIGN_MASK
+#include "Mitchell_32.inl"
+
+extern "C" void ref_direct_mul_bits_array(const uint32_t* at, const uint32_t* bt, uint32_t* out, uint64_t n,
+                                          int mbm) {
+  for (uint64_t i = 0; i < n; ++i) {
+    float a, b;
+    std::memcpy(&a, &at[i], 4);
+    std::memcpy(&b, &bt[i], 4);
+    const float r = mbm ? FPmultMBM_fast32(a, b) : FPmultMitch_fast32(a, b);
+    std::memcpy(&out[i], &r, 4);
+  }
+}

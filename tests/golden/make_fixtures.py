@@ -13,6 +13,9 @@ What it writes, and where each comes from:
   REFERENCE's ``cuda/AMsimulator.inl`` returns for them (compiled as host C++,
   ``oracle/ref_shim.cc``), for every LUT: every exponent class pair in
   {0,1,64,126,127,128,129,200,254,255}^2, both signs, seeded mantissas.
+* ``tests/golden/direct_kat.npz`` — operand bit patterns and the products of the
+  REFERENCE's direct 32-bit models (``cuda/FPmultMBM_fast32.inl``,
+  ``cuda/Mitchell_32.inl``, compiled as host C++ by ``oracle/ref_shim.cc``).
 * ``tests/golden/ops_kat.npz`` — small seeded conv / dense / matmul cases with
   the CPU oracle's outputs (reference GPU semantics), a regression pin for
   the oracle and a GPU-side known-answer test that needs no oracle build.
@@ -67,6 +70,20 @@ def main():
         lut, m = load_lut(os.path.join(gold, "lut", name + ".bin"))
         prim["out_" + name] = refp.mul_bits_array(at, bt, lut, m)
     np.savez_compressed(os.path.join(gold, "prim_kat.npz"), **prim)
+
+    # direct 32-bit models: the reference's cuda/FPmultMBM_fast32.inl and cuda/Mitchell_32.inl as host code
+    from oracle.oracle import DIRECT_MBM32, DIRECT_MIT32
+    rng = np.random.default_rng(77)
+    da = rng.integers(0, 1 << 32, size=20000, dtype=np.uint64).astype(np.uint32)
+    db = rng.integers(0, 1 << 32, size=20000, dtype=np.uint64).astype(np.uint32)
+    # keep most exponents near 127 so that results are ordinary numbers, plus the class grid above
+    da[:16000] = (da[:16000] & np.uint32(0x807FFFFF)) | (rng.integers(100, 156, size=16000).astype(np.uint32) << np.uint32(23))
+    db[:16000] = (db[:16000] & np.uint32(0x807FFFFF)) | (rng.integers(100, 156, size=16000).astype(np.uint32) << np.uint32(23))
+    da = np.concatenate([da, at])
+    db = np.concatenate([db, bt])
+    np.savez_compressed(os.path.join(gold, "direct_kat.npz"), at=da, bt=db,
+                        out_MBM32=refp.direct_mul_bits_array(da, db, DIRECT_MBM32),
+                        out_MIT32=refp.direct_mul_bits_array(da, db, DIRECT_MIT32))
 
     o = Oracle.get()
     rng = np.random.default_rng(2024)

@@ -764,3 +764,57 @@ def test_additive_table_shortcut_is_bit_identical_to_the_table_path(ops, oracle,
             assert_bit_equal(outs["add"][0].cpu().numpy(), oracle.conv2d_fwd(g, x, wt, lut, m), "additive fwd")
             assert_bit_equal(outs["add"][1].cpu().numpy(), oracle.conv2d_bwd_filter(g, x, dy, lut, m), "additive fgrad")
             assert_bit_equal(outs["add"][2].cpu().numpy(), oracle.conv2d_bwd_input(g, wt, dy, lut, m), "additive igrad")
+
+
+@pytest.mark.parametrize("name", ["MBM32", "MIT32"])
+def test_direct_32bit_models(ops, oracle, name):
+    """mant_mul_lut = "direct:MBM32" / "direct:MIT32": the reference's direct C simulation
+    of its 32-bit multipliers (cuda/FPmultMBM_fast32.inl, cuda/Mitchell_32.inl) computed
+    per product inside the same kernels.  The primitive reproduces the committed outputs
+    of the reference's code bit for bit; conv / dense / matmul in every direction equal
+    the oracle bit for bit with either mode flag (one ordered kernel flavour)."""
+    from oracle.oracle import DIRECT_MBM32, DIRECT_MIT32, NO_LUT
+    m = DIRECT_MBM32 if name == "MBM32" else DIRECT_MIT32
+    path = "direct:" + name
+    kat = np.load(os.path.join(GOLDEN, "direct_kat.npz"))
+    at, bt = kat["at"], kat["bt"]
+    got = ops.am_multiply(dev(at.view(np.float32)), dev(bt.view(np.float32)), path).cpu().numpy().view(np.uint32)
+    want = kat["out_" + name]
+    nan = np.isnan(want.view(np.float32))   # a NaN's payload is the host's or the GPU's, not the model's
+    assert np.array_equal(np.isnan(got.view(np.float32)), nan)
+    assert_bit_equal(np.where(nan, 0, got).view(np.float32), np.where(nan, 0, want).view(np.float32),
+                     f"{name} primitive vs reference outputs")
+    rng = np.random.default_rng(123)
+    for (n, h, w, c, kh, kw, k, s, pad) in [(2, 9, 9, 8, 3, 3, 20, 1, "SAME"), (2, 11, 10, 3, 5, 3, 6, 2, "VALID"),
+                                            (1, 12, 12, 16, 3, 3, 70, 2, "SAME")]:
+        x, wt = _conv_case(rng, n, h, w, c, kh, kw, k)
+        g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+        dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+        for det in (True, False):
+            kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=path, deterministic=det)
+            assert_bit_equal(ops.convam(dev(x), dev(wt), **kw_).cpu().numpy(), oracle.conv2d_fwd(g, x, wt, NO_LUT, m), f"{name} fwd")
+            assert_bit_equal(ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_).cpu().numpy(),
+                             oracle.conv2d_bwd_input(g, wt, dy, NO_LUT, m), f"{name} input-grad")
+            assert_bit_equal(ops.convam_filter_grad(wt.shape, dev(x), dev(dy), **kw_).cpu().numpy(),
+                             oracle.conv2d_bwd_filter(g, x, dy, NO_LUT, m), f"{name} filter-grad")
+    xd = rng.standard_normal((37, 50)).astype(np.float32)
+    wd = rng.standard_normal((50, 70)).astype(np.float32)
+    gd = rng.standard_normal((37, 70)).astype(np.float32)
+    assert_bit_equal(ops.denseam(dev(xd), dev(wd), path).cpu().numpy(), oracle.dense_fwd(xd, wd, NO_LUT, m), f"{name} dense")
+    dxd, dwd = ops.denseam_grad(dev(gd), dev(xd), dev(wd), path)
+    assert_bit_equal(dxd.cpu().numpy(), oracle.dense_bwd_input(wd, gd, NO_LUT, m), f"{name} dense dx")
+    assert_bit_equal(dwd.cpu().numpy(), oracle.dense_bwd_weight(xd, gd, NO_LUT, m), f"{name} dense dw")
+    a = rng.standard_normal((3, 10, 21)).astype(np.float32)
+    b = rng.standard_normal((3, 21, 14)).astype(np.float32)
+    assert_bit_equal(ops.matmulam(dev(a), dev(b), mant_mul_lut=path).cpu().numpy(), oracle.matmul(a, b, NO_LUT, m), f"{name} matmul")
+    # inf / NaN pass through, a zero product is +0
+    sp = np.array([np.inf, -np.inf, np.nan, 0.0, -0.0, 1e-45, 3.0], np.float32)
+    A, B = np.meshgrid(sp, sp)
+    got = ops.am_multiply(dev(A.copy()), dev(B.copy()), path).cpu().numpy()
+    want = oracle.mul(A.copy(), B.copy(), NO_LUT, m)
+    assert np.array_equal(got.view(np.uint32) & 0x7F800000, want.view(np.uint32) & 0x7F800000) and \
+        np.array_equal(np.isnan(got), np.isnan(want))
+    with pytest.raises(Exception):
+        ops.am_multiply(dev(A.copy()), dev(B.copy()), "direct:FOO")
+    with pytest.raises(Exception):
+        ops.denseam(dev(xd.astype(np.int32)), dev(wd.astype(np.int32)), path)

@@ -272,3 +272,35 @@ def test_lut_primitive_vs_functional_model_sweep(oracle, luts, name):
     assert normal.sum() > n // 4
     mism = (got != want) & normal
     assert not mism.any(), f"{name}: {mism.sum()} mismatches in the normal range, first at {np.argwhere(mism)[0]}"
+
+
+@pytest.mark.parametrize("name", ["MBM32", "MIT32"])
+def test_direct_32bit_models_match_reference(oracle, name):
+    """The direct simulation of the 32-bit multipliers (no table) against the
+    committed outputs of the reference's cuda/FPmultMBM_fast32.inl /
+    cuda/Mitchell_32.inl, and, when oracle/_ref is built, against that code itself
+    on four million fresh random operand pairs (all exponent classes, NaN/inf,
+    subnormals)."""
+    from oracle.oracle import DIRECT_MBM32, DIRECT_MIT32, NO_LUT, RefPrimitive
+    m = DIRECT_MBM32 if name == "MBM32" else DIRECT_MIT32
+    kat = np.load(os.path.join(GOLDEN, "direct_kat.npz"))
+    got = oracle.mul(kat["at"].view(np.float32), kat["bt"].view(np.float32), NO_LUT, m).view(np.uint32)
+    assert np.array_equal(got, kat["out_" + name])
+    # the approximate product stays within the models' published error of the exact one
+    a, b = kat["at"][:16000].view(np.float32), kat["bt"][:16000].view(np.float32)
+    exact = a.astype(np.float64) * b.astype(np.float64)
+    rel = np.abs(got[:16000].view(np.float32).astype(np.float64) - exact) / np.abs(exact)
+    assert rel.max() < (0.09 if name == "MBM32" else 0.12)
+    if not RefPrimitive.available():
+        pytest.skip("oracle/_ref not built: golden vectors only")
+    ref = RefPrimitive()
+    rng = np.random.default_rng(5)
+    at = rng.integers(0, 1 << 32, size=4_000_000, dtype=np.uint64).astype(np.uint32)
+    bt = rng.integers(0, 1 << 32, size=4_000_000, dtype=np.uint64).astype(np.uint32)
+    ex = np.array([0, 1, 2, 64, 126, 127, 128, 129, 200, 253, 254, 255], np.uint32)
+    at[1::2] = (at[1::2] & np.uint32(0x807FFFFF)) | (rng.choice(ex, size=2_000_000) << np.uint32(23))
+    bt[1::2] = (bt[1::2] & np.uint32(0x807FFFFF)) | (rng.choice(ex, size=2_000_000) << np.uint32(23))
+    at[::7] |= np.uint32(0x7FFFF0)
+    want = ref.direct_mul_bits_array(at, bt, m)
+    got = oracle.mul(at.view(np.float32), bt.view(np.float32), NO_LUT, m).view(np.uint32)
+    assert np.array_equal(got, want)
