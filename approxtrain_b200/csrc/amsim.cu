@@ -257,7 +257,9 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   // partly empty (or never fill them), so the (tile, reduction block) pairs are dealt out in
   // equal runs to exactly as many CTAs as the device holds.  Not taken while the stream is
   // being captured into a graph (the scratch comes from the stream-ordered allocator).
-  if constexpr (!EXACT) {
+  // (not for tables in global memory: those launches are bound by L2 gathers, and lock-step CTAs
+  // measured 50 % slower there)
+  if constexpr (!EXACT && LM != LM_GLOBAL) {
     int rc = ensure_smem(gather_gemm<1, EXACT, VEC, GM_BALANCED, LM>, smem_plain, device);
     if (rc) return rc;
     int slots = 0;
