@@ -10,6 +10,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <set>
@@ -400,7 +401,7 @@ int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
     AMSIM_COUNT_LAUNCH();
-    reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits);
+    reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq);
     CUDA_TRY(cudaGetLastError());
   }
   return AMSIM_OK;
@@ -762,12 +763,45 @@ int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, c
   return AMSIM_OK;
 }
 
+// A weight gradient that is a plain GEMM, dw[k,u] = sum_r AM(x[r,k], g[r,u]) (dense layers; 1x1 stride-1
+// unpadded convolutions, r = pixel): either operand can be the lane operand.  The 128 x 64 tile is filled
+// better with the larger of (in_w, units) along its 128 rows; e.g. 64 -> 256 channels: 64 rows would
+// half-fill the tile, 256 rows fill two.  Swapped, the table is indexed the other way round and the
+// output is written transposed, so every product and every chain is the same.
+static bool wgrad_swap(int in_w, int units) {
+  auto padded = [](long long p, long long q) { return ((p + 127) / 128 * 128) * ((q + BQ - 1) / BQ * BQ); };
+  if (getenv("AMSIM_NO_WGRAD_SWAP")) return false;
+  return padded(units, in_w) < padded(in_w, units);
+}
+
+static void setup_wgrad(Params& p, const amsim_lut* lut, const float* x, const float* g_, float* dw, long long rows,
+                        int in_w, int units, bool swap) {
+  p.V = swap ? g_ : x;
+  p.U = swap ? x : g_;
+  p.O = dw;
+  p.P = swap ? units : in_w;
+  p.Q = swap ? in_w : units;
+  p.K = (int)rows;
+  Gather& g = p.g;
+  g.PH = 1; g.PW = 1; g.ps_h = 1; g.ps_w = 1; g.off_t = 0; g.off_l = 0; g.lim_h = 1; g.lim_w = 1;
+  g.dil_h = 1; g.dil_w = 1; g.SH = 1; g.SW = 1; g.SC = p.P; g.KW = 1;
+  fill_gather_divs(g);
+  p.u_sk = p.Q; p.u_sq = 1;
+  p.o_sp = swap ? 1 : units;
+  p.o_sq = swap ? units : 1;
+  fill_lut(p, lut, /*v_is_first_operand=*/!swap);
+}
+
 size_t amsim_conv2d_bwd_filter_workspace(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c,
                                          int out_h, int out_w, unsigned flags) {
-  (void)in_h; (void)in_w;
   if (batch <= 0 || in_c <= 0 || f_h <= 0 || f_w <= 0 || out_c <= 0 || out_h <= 0 || out_w <= 0) return 0;
   if (flags & AMSIM_INT32) return 0;
-  return plan_fgrad(f_h * f_w * in_c, out_c, batch * out_h * out_w, flags & AMSIM_DETERMINISTIC).ws_bytes;
+  const bool det = flags & AMSIM_DETERMINISTIC;
+  size_t need = plan_fgrad(f_h * f_w * in_c, out_c, batch * out_h * out_w, det).ws_bytes;
+  // a 1x1 stride-1 convolution may run with the operand roles swapped (wgrad_swap): cover both plans
+  if (f_h == 1 && f_w == 1 && out_h == in_h && out_w == in_w && wgrad_swap(in_c, out_c))
+    need = std::max(need, plan_fgrad(out_c, in_c, batch * out_h * out_w, det).ws_bytes);
+  return need;
 }
 
 int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, const float* dy, float* dw, int batch,
@@ -785,6 +819,13 @@ int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, 
     return AMSIM_OK;
   }
   if (!x || !dy) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  if (f_h == 1 && f_w == 1 && stride_h == 1 && stride_w == 1 && pad_top == 0 && pad_left == 0 && out_h == in_h &&
+      out_w == in_w && !(flags & AMSIM_INT32) && wgrad_swap(in_c, out_c)) {
+    // 1x1, stride 1, no padding: dw[c,k] = sum_pixels AM(x[pix,c], dy[pix,k]) is a plain GEMM
+    Params q{};
+    setup_wgrad(q, lut, x, dy, dw, npix, in_c, out_c, /*swap=*/true);
+    return launch_fgrad((cudaStream_t)stream, q, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
+  }
   Params p{};
   p.V = x; p.U = dy; p.O = dw;
   p.P = f_h * f_w * in_c; p.Q = out_c; p.K = (int)npix;
@@ -793,6 +834,7 @@ int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, 
   g.lim_h = in_h; g.lim_w = in_w; g.dil_h = 1; g.dil_w = 1; g.SH = in_h; g.SW = in_w; g.SC = in_c; g.KW = f_w;
   fill_gather_divs(g);
   p.u_sk = out_c; p.u_sq = 1;
+  p.o_sp = out_c; p.o_sq = 1;
   fill_lut(p, lut, true);
   if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, true);
   return launch_fgrad((cudaStream_t)stream, p, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
@@ -906,6 +948,7 @@ int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w, co
 size_t amsim_dense_bwd_weight_workspace(int batch, int units, int input_width, unsigned flags) {
   if (batch <= 0 || units <= 0 || input_width <= 0) return 0;
   if (flags & AMSIM_INT32) return 0;
+  if (wgrad_swap(input_width, units)) return plan_fgrad(units, input_width, batch, flags & AMSIM_DETERMINISTIC).ws_bytes;
   return plan_fgrad(input_width, units, batch, flags & AMSIM_DETERMINISTIC).ws_bytes;
 }
 
@@ -923,14 +966,7 @@ int amsim_dense_bwd_weight(void* stream, const amsim_lut* lut, const float* x, c
   // dw[k,u] = sum_b AM(x[b,k], g[b,u]) — the filter gradient of a 1x1
   // convolution over a batch x 1 x 1 grid.
   Params p{};
-  p.V = x; p.U = g_; p.O = dw;
-  p.P = input_width; p.Q = units; p.K = batch;
-  Gather& g = p.g;
-  g.PH = 1; g.PW = 1; g.ps_h = 1; g.ps_w = 1; g.off_t = 0; g.off_l = 0; g.lim_h = 1; g.lim_w = 1;
-  g.dil_h = 1; g.dil_w = 1; g.SH = 1; g.SW = 1; g.SC = input_width; g.KW = 1;
-  fill_gather_divs(g);
-  p.u_sk = units; p.u_sq = 1;
-  fill_lut(p, lut, true);
+  setup_wgrad(p, lut, x, g_, dw, batch, input_width, units, !(flags & AMSIM_INT32) && wgrad_swap(input_width, units));
   if (flags & AMSIM_INT32) return launch_naive_i32((cudaStream_t)stream, p, lut, true);
   return launch_fgrad((cudaStream_t)stream, p, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
 }

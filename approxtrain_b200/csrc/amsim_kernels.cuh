@@ -789,13 +789,16 @@ AMSIM_UNROLL_K
     __syncthreads();
   }
 
-  float* __restrict__ Og = prm.splits > 1 ? prm.ws + (long long)blockIdx.z * ((long long)prm.P * prm.Q) : prm.O;
-  const bool vec_out = (prm.Q & 3) == 0 && ((reinterpret_cast<uintptr_t>(Og) & 15) == 0);
+  // partial sums go to ws[split][P][Q]; a single split writes Out[p * o_sp + q * o_sq] itself
+  const bool to_ws = prm.splits > 1;
+  float* __restrict__ Og = to_ws ? prm.ws + (long long)blockIdx.z * ((long long)prm.P * prm.Q) : prm.O;
+  const long long sp = to_ws ? prm.Q : prm.o_sp, sq = to_ws ? 1 : prm.o_sq;
+  const bool vec_out = sq == 1 && (sp & 3) == 0 && ((reinterpret_cast<uintptr_t>(Og) & 15) == 0);
 #pragma unroll
   for (int c = 0; c < TC; ++c) {
     const int pg = p0 + vcol + c;
     if (pg >= prm.P) continue;
-    float* orow = Og + (long long)pg * prm.Q;
+    float* orow = Og + (long long)pg * sp;
 #pragma unroll
     for (int g4 = 0; g4 < TR / 4; ++g4) {
       const int qg = q0 + ucol + 4 * g4;
@@ -805,7 +808,7 @@ AMSIM_UNROLL_K
       } else {
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-          if (qg + r < prm.Q) orow[qg + r] = acc[4 * g4 + r][c];
+          if (qg + r < prm.Q) orow[(long long)(qg + r) * sq] = acc[4 * g4 + r][c];
       }
     }
   }
@@ -933,19 +936,22 @@ __global__ void __launch_bounds__(128) fgrad_exact_thin(const Params prm) {
 #pragma unroll
     for (int r = 0; r < TQ; ++r) {
       const int qg = q0 + w * TQ + r;
-      if (qg < prm.Q) prm.O[(long long)pg * prm.Q + qg] = acc[r];
+      if (qg < prm.Q) prm.O[(long long)pg * prm.o_sp + (long long)qg * prm.o_sq] = acc[r];
     }
   }
 }
 
 // Sums the split-K partials in ascending split order (fixed order: the result
 // does not depend on scheduling).
-__global__ void reduce_splits(const float* __restrict__ ws, float* __restrict__ out, long long n, int splits) {
+// Partials are [split][P][Q]; the sum goes to out[p * o_sp + q * o_sq].
+__global__ void reduce_splits(const float* __restrict__ ws, float* __restrict__ out, long long n, int splits, int Q,
+                              long long o_sp, long long o_sq) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float s = ws[i];
   for (int k = 1; k < splits; ++k) s = __fadd_rn(s, ws[(long long)k * n + i]);
-  out[i] = s;
+  const long long p = i / Q, q = i - p * Q;
+  out[p * o_sp + q * o_sq] = s;
 }
 
 // The reference primitive on raw LUT bytes (cuda/AMsimulator.inl:13-36).

@@ -818,3 +818,38 @@ def test_direct_32bit_models(ops, oracle, name):
         ops.am_multiply(dev(A.copy()), dev(B.copy()), "direct:FOO")
     with pytest.raises(Exception):
         ops.denseam(dev(xd.astype(np.int32)), dev(wd.astype(np.int32)), path)
+
+
+@pytest.mark.parametrize("noswap", [None, "1"])
+def test_weight_gradient_with_swapped_operand_roles(ops, oracle, luts, noswap, monkeypatch):
+    """GEMM-shaped weight gradients (dense; 1x1 stride-1 convolutions) with few inputs and
+    many outputs run with the gradient as the lane operand and the input as the uniform
+    one, the table indexed the other way round and the output written transposed: same
+    products, same chains.  Deterministic bit-exact, fast within the bar, asymmetric LUT."""
+    if noswap:
+        monkeypatch.setenv("AMSIM_NO_WGRAD_SWAP", noswap)
+    rng = np.random.default_rng(64)
+    lut = rng.integers(0, 256, size=1 << 10, dtype=np.uint8)   # m = 5, not symmetric
+    from approxtrain_b200 import _lib
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "ASYM_5.bin")
+        lut.tofile(path)
+        for name, (lt, m, pth) in {"asym": (lut, 5, path), "MBM_7": luts["MBM_7"] + (lut_path("MBM_7"),)}.items():
+            x, _ = _conv_case(rng, 3, 10, 10, 64, 1, 1, 256)
+            g = oracle.geometry(3, 10, 10, 64, 1, 1, 256, 1, 1, "VALID")
+            dy = rng.standard_normal((3, 10, 10, 256)).astype(np.float32)
+            want = oracle.conv2d_bwd_filter(g, x, dy, lt, m)
+            kw_ = dict(strides=[1, 1, 1, 1], padding="VALID", mant_mul_lut=pth)
+            got = ops.convam_filter_grad((1, 1, 64, 256), dev(x), dev(dy), deterministic=True, **kw_).cpu().numpy()
+            assert_bit_equal(got, want, f"1x1 filter-grad det {name} noswap={noswap}")
+            got = ops.convam_filter_grad((1, 1, 64, 256), dev(x), dev(dy), **kw_).cpu().numpy()
+            assert_close(got, want, f"1x1 filter-grad fast {name} noswap={noswap}")
+            xd = rng.standard_normal((300, 40)).astype(np.float32)
+            wd = rng.standard_normal((40, 200)).astype(np.float32)
+            gd = rng.standard_normal((300, 200)).astype(np.float32)
+            wantd = oracle.dense_bwd_weight(xd, gd, lt, m)
+            _, dwd = ops.denseam_grad(dev(gd), dev(xd), dev(wd), pth, deterministic=True)
+            assert_bit_equal(dwd.cpu().numpy(), wantd, f"dense weight-grad det {name} noswap={noswap}")
+            _, dwd = ops.denseam_grad(dev(gd), dev(xd), dev(wd), pth)
+            assert_close(dwd.cpu().numpy(), wantd, f"dense weight-grad fast {name} noswap={noswap}")
