@@ -190,6 +190,7 @@ void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
   p.lut_mode = lut->direct ? lut->direct : lut->m > 7 ? LM_GLOBAL : (lut->additive ? LM_ADD : LM_SMEM);
   p.lut_raw = v_is_first_operand ? lut->d_raw_t : lut->d_raw;
   p.v_first = v_is_first_operand ? 1 : 0;
+  p.exact_only = getenv("AMSIM_EXACT_ONLY") != nullptr;
   uint32_t al = 16;
   while (al < (uint32_t)lut->enc_bytes) al <<= 1;
   p.lut_align = al;  // m > 7: no table in shared memory (enc_bytes = 0)

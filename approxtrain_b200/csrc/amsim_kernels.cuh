@@ -141,6 +141,7 @@ struct Params {
   // gather_gemm, matmul with a transposed first operand: V[p, k] sits at V[k * v_ld + p]
   int v_trans;
   long long v_ld;
+  int exact_only;               // deterministic kernels: never take the fast arithmetic, even for hazard-free stages
   // fgrad only
   int k_chunk, splits;
   float* ws;                    // [splits][P][Q] partial sums when splits > 1
@@ -230,13 +231,35 @@ __device__ __forceinline__ uint32_t enc_v(uint32_t bits, int m) {
   return (bits & 0x7F800000u) ? w : 0u;
 }
 
+// Deterministic mode on fast arithmetic.  The fast inner loop (IMAD + FFMA) produces the
+// reference's bits whenever no product of a stage can hit one of the reference's special
+// behaviours: exponent sum <= 127 (the reference returns 0), exponent overflow (it wraps into
+// the sign), or an exponent-0 operand meeting an operand >= 2 (it returns a non-zero residue).
+// Staging collects, per stage, whether any operand lies outside a window that rules all of
+// that out; a stage with a hazard runs the bit-by-bit loop instead.  Typical activations,
+// weights and gradients (magnitudes 2^-63 .. 2^63, zeros) never leave the window.
+constexpr uint32_t HZ_V0 = 1u, HZ_VBIG = 2u, HZ_U0 = 4u, HZ_UBIG = 8u, HZ_OUT = 16u;
+__device__ __forceinline__ uint32_t hazard_bits(uint32_t bits, bool is_u) {
+  const uint32_t e = (bits >> 23) & 0xFFu;
+  uint32_t h = 0;
+  if (e == 0u) h |= is_u ? HZ_U0 : HZ_V0;
+  else if (e - 64u > 126u) h |= HZ_OUT;            // outside [64, 190]
+  if (e >= 128u) h |= is_u ? HZ_UBIG : HZ_VBIG;
+  return h;
+}
+__device__ __forceinline__ bool hazard_free(uint32_t h) {
+  return !(h & HZ_OUT) && !((h & HZ_V0) && (h & HZ_UBIG)) && !((h & HZ_U0) && (h & HZ_VBIG));
+}
+
 // One reduction step of a 16 (q) x 4 (p) register tile.
 //   vrow : 4 consecutive lane-operand words (sign+exponent | column)
 //   urow : 16 uniform-operand words (sign+exponent | column << m)
 //   lut_base : shared-memory address of the table (aligned to its size)
 //   LM   : LM_SMEM table in shared memory at lut_base; LM_GLOBAL raw table in global
 //          memory at lut_g; LM_ADD no table (additive: an integer add of mantissa fields).
-template <bool EXACT, int LM>
+// NZEXP: the lane words carry the deterministic encoding (exponent-0 operands keep their
+// fields), so "operand is zero" is read from the exponent field instead of the whole word.
+template <bool EXACT, int LM, bool NZEXP = false>
 __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* __restrict__ vrow,
                                          const uint32_t* __restrict__ urow, const uint32_t lut_base,
                                          const uint32_t rmask, const uint32_t mult, const uint32_t cmask,
@@ -249,7 +272,7 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
 #pragma unroll
   for (int t = 0; t < TC; ++t) {
     ci[t] = LM == LM_GLOBAL ? (w[t] & cmask) : ((w[t] & 0xFFu) | lut_base);
-    nz[t] = w[t] != 0u;
+    nz[t] = NZEXP ? (w[t] & 0x7F800000u) != 0u : w[t] != 0u;
     if (EXACT) {
       // AMsimulator.inl:26-33: exponent sum - 127, folded into the lane word
       // (additive table: the word's mantissa field stays in, it IS the table term)
@@ -322,7 +345,8 @@ struct SmemLayout {
   static constexpr int VS = BP + 4;  // padded row: conflict-free 4-row scatter
   static constexpr int V_WORDS = 2 * BK * VS;
   static constexpr int U_WORDS = 2 * BK * US;
-  static constexpr int TILE_BYTES = (V_WORDS + U_WORDS) * 4;
+  static constexpr int FLAG_WORDS = 2 * 4 * WP;  // deterministic kernels: one hazard word per stage and warp
+  static constexpr int TILE_BYTES = (V_WORDS + U_WORDS + FLAG_WORDS) * 4;
   // tiles, then the table at the next multiple of its alignment
   static constexpr int EXCHANGE_BYTES = TR * TC * NT * 4;  // one register tile per thread
   static size_t bytes(int tile_bytes, int lut_bytes, int lut_align) { return (size_t)tile_bytes + lut_align + lut_bytes; }
@@ -390,6 +414,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   extern __shared__ __align__(16) uint8_t smem[];
   uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);
   uint32_t* Us = Vs + L::V_WORDS;
+  uint32_t* Fs = Us + L::U_WORDS;  // per stage and warp: hazard bits of the staged operands
+  constexpr bool HAZARD_CHECK = EXACT && !lm_direct(LM);
   const uint32_t smem_base = smem_addr(smem);
   const uint32_t lut_base = (smem_base + prm.tile_bytes + prm.lut_align - 1) & ~(prm.lut_align - 1);
   uint8_t* lut_s = smem + (lut_base - smem_base);
@@ -525,6 +551,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 
   auto store_tile = [&](int buf) {
     uint32_t* vs = Vs + buf * BK * VS;
+    uint32_t hz = 0;
 #pragma unroll
     for (int ik = 0; ik < 2; ++ik) {
       const int krow = 4 * (2 * ik + kg_sub);
@@ -535,6 +562,9 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
         vs[(krow + 1) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.y), prm.m);
         vs[(krow + 2) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.z), prm.m);
         vs[(krow + 3) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.w), prm.m);
+        if (HAZARD_CHECK)
+          hz |= hazard_bits(__float_as_uint(f.x), false) | hazard_bits(__float_as_uint(f.y), false) |
+                hazard_bits(__float_as_uint(f.z), false) | hazard_bits(__float_as_uint(f.w), false);
       }
     }
 #pragma unroll
@@ -543,6 +573,11 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
       const int kl = u_kmajor ? (e & (BK - 1)) : (e >> 6);
       const int ql = u_kmajor ? (e >> 4) : (e & 63);
       Us[buf * BK * US + kl * US + ql] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
+      if (HAZARD_CHECK) hz |= hazard_bits(__float_as_uint(uraw[j]), true);
+    }
+    if (HAZARD_CHECK) {
+      hz = __reduce_or_sync(0xffffffffu, hz);
+      if (lane == 0) Fs[buf * 4 * WP + w] = hz;
     }
   };
 
@@ -566,10 +601,27 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
     if (kb + 1 < nkb) load_tile(kb + 1);
     const uint32_t* vs = Vs + buf * BK * VS + vcol;
     const uint32_t* us = Us + buf * BK * US + ucol;
+    if (HAZARD_CHECK) {
+      uint32_t hz = 0;
+#pragma unroll
+      for (int i = 0; i < 4 * WP; ++i) hz |= Fs[buf * 4 * WP + i];
+      if (hazard_free(hz) && !prm.exact_only) {
 AMSIM_UNROLL_K
-    for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+        for (int kk = 0; kk < BK; ++kk)
+          mac_step<false, LM, true>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask,
+                                    prm.cadj, prm.lut_raw);
+      } else {
+AMSIM_UNROLL_K
+        for (int kk = 0; kk < BK; ++kk)
+          mac_step<true, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+                             prm.lut_raw);
+      }
+    } else {
+AMSIM_UNROLL_K
+      for (int kk = 0; kk < BK; ++kk)
+        mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
                             prm.lut_raw);
+    }
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }
@@ -672,6 +724,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
   extern __shared__ __align__(16) uint8_t smem[];
   uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);
   uint32_t* Us = Vs + L::V_WORDS;
+  uint32_t* Fs = Us + L::U_WORDS;  // per stage and warp: hazard bits of the staged operands
+  constexpr bool HAZARD_CHECK = EXACT && !lm_direct(LM);
   const uint32_t smem_base = smem_addr(smem);
   const uint32_t lut_base = (smem_base + L::TILE_BYTES + prm.lut_align - 1) & ~(prm.lut_align - 1);
   uint8_t* lut_s = smem + (lut_base - smem_base);
@@ -745,6 +799,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
 
   auto store_tile = [&](int buf) {
     uint32_t* vs = Vs + buf * BK * VS;
+    uint32_t hz = 0;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const float4 f = vraw[i];
@@ -754,11 +809,19 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
       wv.z = enc_v<EXACT, LM>(__float_as_uint(f.z), prm.m);
       wv.w = enc_v<EXACT, LM>(__float_as_uint(f.w), prm.m);
       *reinterpret_cast<uint4*>(vs + (i * RPP + krow0) * VS + pl) = wv;
+      if (HAZARD_CHECK)
+        hz |= hazard_bits(__float_as_uint(f.x), false) | hazard_bits(__float_as_uint(f.y), false) |
+              hazard_bits(__float_as_uint(f.z), false) | hazard_bits(__float_as_uint(f.w), false);
     }
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
       Us[buf * BK * US + (e >> 6) * US + (e & 63)] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
+      if (HAZARD_CHECK) hz |= hazard_bits(__float_as_uint(uraw[j]), true);
+    }
+    if (HAZARD_CHECK) {
+      hz = __reduce_or_sync(0xffffffffu, hz);
+      if (lane == 0) Fs[buf * 4 * WP + w] = hz;
     }
   };
 
@@ -781,10 +844,27 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
     if (kb + 1 < nkb) load_tile(kb + 1);
     const uint32_t* vs = Vs + buf * BK * VS + vcol;
     const uint32_t* us = Us + buf * BK * US + ucol;
+    if (HAZARD_CHECK) {
+      uint32_t hz = 0;
+#pragma unroll
+      for (int i = 0; i < 4 * WP; ++i) hz |= Fs[buf * 4 * WP + i];
+      if (hazard_free(hz) && !prm.exact_only) {
 AMSIM_UNROLL_K
-    for (int kk = 0; kk < BK; ++kk)
-      mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+        for (int kk = 0; kk < BK; ++kk)
+          mac_step<false, LM, true>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask,
+                                    prm.cadj, prm.lut_raw);
+      } else {
+AMSIM_UNROLL_K
+        for (int kk = 0; kk < BK; ++kk)
+          mac_step<true, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+                             prm.lut_raw);
+      }
+    } else {
+AMSIM_UNROLL_K
+      for (int kk = 0; kk < BK; ++kk)
+        mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
                             prm.lut_raw);
+    }
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }

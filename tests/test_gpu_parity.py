@@ -853,3 +853,55 @@ def test_weight_gradient_with_swapped_operand_roles(ops, oracle, luts, noswap, m
             assert_bit_equal(dwd.cpu().numpy(), wantd, f"dense weight-grad det {name} noswap={noswap}")
             _, dwd = ops.denseam_grad(dev(gd), dev(xd), dev(wd), pth)
             assert_close(dwd.cpu().numpy(), wantd, f"dense weight-grad fast {name} noswap={noswap}")
+
+
+@pytest.mark.parametrize("exact_only", [None, "1"])
+def test_deterministic_mode_hazard_stages(ops, oracle, luts, exact_only, monkeypatch):
+    """Deterministic kernels run a stage on the fast arithmetic when none of its operands can
+    reach one of the reference's special behaviours, and bit by bit otherwise.  Data that
+    mixes ordinary values with every hazard (zeros next to operands >= 2, magnitudes below
+    2^-63 and above 2^63, denormals, exponent sums <= 127, overflow into the sign bit) stays
+    bit-identical to the oracle in all three directions, with the fast arithmetic allowed
+    and with it switched off."""
+    if exact_only:
+        monkeypatch.setenv("AMSIM_EXACT_ONLY", exact_only)
+    monkeypatch.setenv("AMSIM_THIN_FGRAD", "0")   # the tiled filter-gradient kernel is the one with the two loops
+    rng = np.random.default_rng(2718)
+
+    def spice(a, frac=0.08):
+        a = a.copy().reshape(-1)
+        n = a.size
+        specials = np.array([0.0, -0.0, 2.5, -3.0, 1e-30, -1e-25, 1e25, -3e30, 1e-40, 6e-39, 1e38, -2e38,
+                             2.0 ** -63, 2.0 ** 63, 2.0 ** -64, 2.0 ** 64], np.float32)
+        idx = rng.choice(n, size=max(1, int(n * frac)), replace=False)
+        a[idx] = rng.choice(specials, size=idx.size)
+        return a
+
+    for name in ("MBM_7", "MIT_7", "MBM_3"):
+        lut, m = luts[name]
+        path = lut_path(name)
+        for (n, h, w, c, kh, kw, k, s, pad) in [(2, 9, 9, 8, 3, 3, 20, 1, "SAME"), (1, 12, 12, 16, 3, 3, 70, 2, "SAME")]:
+            x, wt = _conv_case(rng, n, h, w, c, kh, kw, k)
+            g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+            dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+            for variant in range(3):
+                # 0: hazards everywhere; 1: only in a corner of x (most stages hazard-free); 2: none
+                xs, ws, ds = x, wt, dy
+                if variant == 0:
+                    xs, ws, ds = spice(x).reshape(x.shape), spice(wt).reshape(wt.shape), spice(dy).reshape(dy.shape)
+                elif variant == 1:
+                    xs = x.copy()
+                    xs[0, :2, :2, :] = spice(xs[0, :2, :2, :], 0.5).reshape(xs[0, :2, :2, :].shape)
+                kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=path, deterministic=True)
+                with np.errstate(all="ignore"):
+                    want_y = oracle.conv2d_fwd(g, xs, ws, lut, m)
+                    want_dx = oracle.conv2d_bwd_input(g, ws, ds, lut, m)
+                    want_dw = oracle.conv2d_bwd_filter(g, xs, ds, lut, m)
+                def same(got, want, what):
+                    got = got.cpu().numpy()
+                    nan = np.isnan(want)
+                    assert np.array_equal(np.isnan(got), nan), what
+                    assert_bit_equal(np.where(nan, 0, got), np.where(nan, 0, want), what)
+                same(ops.convam(dev(xs), dev(ws), **kw_), want_y, f"{name} fwd v{variant}")
+                same(ops.convam_input_grad(xs.shape, dev(ws), dev(ds), **kw_), want_dx, f"{name} input-grad v{variant}")
+                same(ops.convam_filter_grad(ws.shape, dev(xs), dev(ds), **kw_), want_dw, f"{name} filter-grad v{variant}")
