@@ -497,8 +497,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
           float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
           const int u = r0[ip] + kh, v = c0[ip] + kw;
           if (pv[ip] && kglob < prm.K && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
-            const int row = (int)fdiv((uint32_t)u, g.d_dh), col = (int)fdiv((uint32_t)v, g.d_dw);
-            if (row * g.dil_h == u && col * g.dil_w == v)
+            // only the deterministic input gradient gathers a stride-dilated tensor (fast mode runs
+            // one sub-convolution per stride phase instead)
+            const int row = EXACT ? (int)fdiv((uint32_t)u, g.d_dh) : u, col = EXACT ? (int)fdiv((uint32_t)v, g.d_dw) : v;
+            if (!EXACT || (row * g.dil_h == u && col * g.dil_w == v))
               val = __ldg(reinterpret_cast<const float4*>(Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch)));
           }
           vraw[ik][ip] = val;
@@ -519,8 +521,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
             if (prm.v_trans) {
               if (pv[ip] && kj < prm.K) val = __ldg(Vg + (long long)kj * prm.v_ld + (p0 + pl[ip]));
             } else if (pv[ip] && kj < prm.K && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
-              const int row = (int)fdiv((uint32_t)u, g.d_dh), col = (int)fdiv((uint32_t)v, g.d_dw);
-              if (row * g.dil_h == u && col * g.dil_w == v)
+              const int row = EXACT ? (int)fdiv((uint32_t)u, g.d_dh) : u, col = EXACT ? (int)fdiv((uint32_t)v, g.d_dw) : v;
+              if (!EXACT || (row * g.dil_h == u && col * g.dil_w == v))
                 val = __ldg(Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch));
             }
             tmp[ip][j] = val;
