@@ -283,19 +283,20 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
       p.sk_ptiles = ptiles;
       p.sk_qtiles = qtiles;
       p.sk_grid = (int)grid;
-      const size_t bytes = (size_t)grid * 2 * TR * TC * L::NT * sizeof(float);
+      const size_t slot_bytes = (size_t)grid * 2 * TR * TC * L::NT * sizeof(float);
+      const size_t bytes = slot_bytes + (size_t)ctas * sizeof(int);
       rc = scratch_alloc(st, device, bytes, &p.ws);
       if (rc) return rc;
-      AMSIM_COUNT_LAUNCH();
-      gather_gemm<1, EXACT, VEC, GM_BALANCED, LM><<<dim3((unsigned)grid), L::NT, smem_plain, st>>>(p);
-      cudaError_t e1 = cudaGetLastError();
+      p.sk_count = reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) + slot_bytes);
+      cudaError_t e1 = cudaMemsetAsync(p.sk_count, 0, (size_t)ctas * sizeof(int), st);
       if (e1 == cudaSuccess) {
         AMSIM_COUNT_LAUNCH();
-        gather_combine<1><<<dim3((unsigned)ctas), L::NT, 0, st>>>(p);
+        gather_gemm<1, EXACT, VEC, GM_BALANCED, LM><<<dim3((unsigned)grid), L::NT, smem_plain, st>>>(p);
         e1 = cudaGetLastError();
       }
       cudaError_t e2 = cudaFreeAsync(p.ws, st);
       p.ws = nullptr;
+      p.sk_count = nullptr;
       CUDA_TRY(e1);
       CUDA_TRY(e2);
       return AMSIM_OK;

@@ -151,6 +151,7 @@ struct Params {
   long long sk_iters;           // tiles * reduction blocks per tile
   int sk_ptiles, sk_qtiles;     // tile grid (q runs fastest, then p, then batch)
   int sk_grid;                  // CTAs of the balanced launch
+  int* sk_count;                // per tile: CTAs that have parked their share (zero before the launch)
 };
 
 __device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
@@ -429,6 +430,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 
   if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
 
+  uint32_t* flag_s = Fs;  // balanced mode (fast kernels only, where Fs is otherwise unused): "this CTA completes the tile"
   // Balanced mode: this CTA's run of (tile, reduction block) pairs; otherwise one pass.
   long long run_at = 0, run_end = 0;
   if (BALANCED) {
@@ -654,57 +656,53 @@ AMSIM_UNROLL_K
     if (krank != 0) return;
   }
 
-  // ---- balanced mode: a tile whose reduction this CTA only shares parks its register
-  // tile in the workspace (slot 0: the run started inside the tile, slot 1: it started the tile)
+  // ---- balanced mode: a tile whose reduction this CTA only shares parks its register tile in
+  // the workspace (slot 0: the run started inside the tile, slot 1: it started the tile) and
+  // counts itself in; the CTA that completes the count adds all parked tiles of the tile in
+  // CTA order (whoever it is, the order is the same) and writes the output.  Nobody waits.
   if (BALANCED && (kb_begin != 0 || nkb != nkb_all)) {
     float* slot = prm.ws + ((long long)blockIdx.x * 2 + (kb_begin == 0 ? 1 : 0)) * (TR * TC * NT);
 #pragma unroll
     for (int r = 0; r < TR; ++r)
 #pragma unroll
-      for (int c = 0; c < TC; ++c) slot[(r * TC + c) * NT + t] = acc[r][c];
+      for (int c = 0; c < TC; ++c) __stcg(slot + (r * TC + c) * NT + t, acc[r][c]);
+    __threadfence();  // this thread's part of the tile is visible device-wide before the count
+    __syncthreads();
+    const long long tile = ((long long)tile_z * prm.sk_ptiles + tile_p) * prm.sk_qtiles + tile_q;
+    const long long first = tile * nkb_all, last = first + nkb_all;
+    long long c0 = first * prm.sk_grid / prm.sk_iters;   // CTA whose run holds the tile's first block
+    while (c0 > 0 && balanced_begin(c0, prm.sk_iters, prm.sk_grid) > first) --c0;
+    while (balanced_begin(c0 + 1, prm.sk_iters, prm.sk_grid) <= first) ++c0;
+    long long c1 = (last - 1) * prm.sk_grid / prm.sk_iters;  // ... and its last block
+    while (c1 > 0 && balanced_begin(c1, prm.sk_iters, prm.sk_grid) > last - 1) --c1;
+    while (balanced_begin(c1 + 1, prm.sk_iters, prm.sk_grid) <= last - 1) ++c1;
+    if (t == 0) {
+      const int arrived = atomicAdd(prm.sk_count + tile, 1);
+      *flag_s = arrived == (int)(c1 - c0);  // c1 - c0 + 1 sharers
+    }
+    __syncthreads();
+    const bool completes = *flag_s != 0;
+    __syncthreads();  // flag_s may be rewritten by the next segment
+    if (completes) {
+      __threadfence();
+#pragma unroll
+      for (int r = 0; r < TR; ++r)
+#pragma unroll
+        for (int c = 0; c < TC; ++c) acc[r][c] = 0.f;
+      for (long long cta = c0; cta <= c1; ++cta) {
+        const long long b = balanced_begin(cta, prm.sk_iters, prm.sk_grid);
+        const float* src = prm.ws + (cta * 2 + (b <= first ? 1 : 0)) * (TR * TC * NT);
+#pragma unroll
+        for (int r = 0; r < TR; ++r)
+#pragma unroll
+          for (int c = 0; c < TC; ++c) acc[r][c] = __fadd_rn(acc[r][c], __ldcg(src + (r * TC + c) * NT + t));
+      }
+      store_out_tile(prm, acc, Og, p0 + vcol, q0 + ucol);
+    }
   } else {
     store_out_tile(prm, acc, Og, p0 + vcol, q0 + ucol);
   }
   } while (BALANCED && run_at < run_end);
-}
-
-// Second pass of a balanced gather_gemm launch: one CTA per tile adds the parked register
-// tiles of the CTAs that shared the tile's reduction, in CTA order, and writes the output.
-// Tiles reduced by a single CTA were written by gather_gemm itself.
-template <int WP>
-__global__ void __launch_bounds__(WP * 128) gather_combine(const Params prm) {
-  using L = SmemLayout<WP>;
-  constexpr int NT = L::NT, BP = L::BP;
-  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
-  const int wp = w % WP, wq = w / WP;
-  const int nkb_all = (prm.K + BK - 1) / BK;
-  const long long tile = blockIdx.x;
-  const long long first = tile * nkb_all, last = first + nkb_all;
-  long long c = first * prm.sk_grid / prm.sk_iters;
-  while (c > 0 && balanced_begin(c, prm.sk_iters, prm.sk_grid) > first) --c;
-  while (balanced_begin(c + 1, prm.sk_iters, prm.sk_grid) <= first) ++c;
-  if (balanced_begin(c + 1, prm.sk_iters, prm.sk_grid) >= last) return;  // one CTA had the whole tile
-
-  float acc[TR][TC];
-#pragma unroll
-  for (int r = 0; r < TR; ++r)
-#pragma unroll
-    for (int k = 0; k < TC; ++k) acc[r][k] = 0.f;
-  for (; c < prm.sk_grid; ++c) {
-    const long long b = balanced_begin(c, prm.sk_iters, prm.sk_grid);
-    if (b >= last) break;
-    if (balanced_begin(c + 1, prm.sk_iters, prm.sk_grid) == b) continue;  // empty run
-    const float* slot = prm.ws + (c * 2 + (b <= first ? 1 : 0)) * (TR * TC * NT);
-#pragma unroll
-    for (int r = 0; r < TR; ++r)
-#pragma unroll
-      for (int k = 0; k < TC; ++k) acc[r][k] = __fadd_rn(acc[r][k], slot[(r * TC + k) * NT + t]);
-  }
-  const int tile_q = (int)(tile % prm.sk_qtiles);
-  const long long rest = tile / prm.sk_qtiles;
-  const int tile_p = (int)(rest % prm.sk_ptiles), tile_z = (int)(rest / prm.sk_ptiles);
-  float* __restrict__ Og = prm.O + (long long)tile_z * prm.o_bs;
-  store_out_tile(prm, acc, Og, tile_p * BP + wp * 128 + 4 * lane, tile_q * BQ + wq * TR);
 }
 
 // -----------------------------------------------------------------------------
