@@ -346,6 +346,14 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
   if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
   if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");
   const bool vec = !p.v_trans && (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
+  // U by 128-bit loads along its contiguous index when four elements are always one aligned
+  // group inside one tap: along q (weights of a forward convolution / dense layer / matmul B),
+  // or along k (flipped filter of an input gradient, transposed matmul B)
+  p.u_vec = 0;
+  if (aligned16(p.U) && p.u_bs % 4 == 0 && p.u_tap % 4 == 0 && !getenv("AMSIM_NO_UVEC")) {
+    if (p.u_sq == 1 && p.u_sk % 4 == 0 && p.Q % 4 == 0) p.u_vec = 1;
+    else if (p.u_sk == 1 && p.u_sq % 4 == 0 && p.g.SC % 4 == 0) p.u_vec = 2;
+  }
 #define AMSIM_GO(EX_, VEC_, LM_) return launch_gather_t<EX_, VEC_, LM_>(st, p, batch, device)
 #define AMSIM_GO_LM(LM_)                                                                        \
   do {                                                                                          \

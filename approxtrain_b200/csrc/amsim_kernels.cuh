@@ -141,6 +141,7 @@ struct Params {
   // gather_gemm, matmul with a transposed first operand: V[p, k] sits at V[k * v_ld + p]
   int v_trans;
   long long v_ld;
+  int u_vec;                    // gather_gemm: 128-bit loads of U along q (1) or along k (2); 0 = scalar
   int exact_only;               // deterministic kernels: never take the fast arithmetic, even for hazard-free stages
   // fgrad only
   int k_chunk, splits;
@@ -534,6 +535,27 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
         for (int ip = 0; ip < 2; ++ip) vraw[ik][ip] = make_float4(tmp[ip][0], tmp[ip][1], tmp[ip][2], tmp[ip][3]);
       }
     }
+    if (prm.u_vec) {
+      // 128-bit loads along the contiguous index (q: u_vec 1, k: u_vec 2); the host has checked
+      // alignment and that a group of four never straddles a tap or the end of the tensor
+#pragma unroll
+      for (int j = 0; j < NU / 4; ++j) {
+        const int f = j * NT + t;
+        const int kl = prm.u_vec == 2 ? (f & 3) * 4 : (f >> 4);
+        const int ql = prm.u_vec == 2 ? (f >> 2) : (f & 15) * 4;
+        const int kglob = kb * BK + kl, qg = q0 + ql;
+        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (kglob < prm.K && qg < prm.Q) {
+          const uint32_t tap = fdiv((uint32_t)kglob, g.d_sc);
+          const int kk = kglob - (int)tap * g.SC;
+          const int tj = (int)fdiv(tap, g.d_kw);
+          const int tp = prm.u_t0 + tj * prm.u_tj + ((int)tap - tj * g.KW) * prm.u_ti;
+          val = __ldg(reinterpret_cast<const float4*>(Ug + (long long)tp * prm.u_tap + (long long)kk * prm.u_sk +
+                                                      (long long)qg * prm.u_sq));
+        }
+        uraw[4 * j] = val.x; uraw[4 * j + 1] = val.y; uraw[4 * j + 2] = val.z; uraw[4 * j + 3] = val.w;
+      }
+    } else {
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
@@ -550,6 +572,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
         val = __ldg(Ug + (long long)tp * prm.u_tap + (long long)kk * prm.u_sk + (long long)qg * prm.u_sq);
       }
       uraw[j] = val;
+    }
     }
   };
 
@@ -571,13 +594,34 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
                 hazard_bits(__float_as_uint(f.z), false) | hazard_bits(__float_as_uint(f.w), false);
       }
     }
+    if (prm.u_vec) {
+#pragma unroll
+      for (int j = 0; j < NU / 4; ++j) {
+        const int f = j * NT + t;
+        uint4 wu;
+        wu.x = enc_u<LM>(__float_as_uint(uraw[4 * j]), prm.m);
+        wu.y = enc_u<LM>(__float_as_uint(uraw[4 * j + 1]), prm.m);
+        wu.z = enc_u<LM>(__float_as_uint(uraw[4 * j + 2]), prm.m);
+        wu.w = enc_u<LM>(__float_as_uint(uraw[4 * j + 3]), prm.m);
+        if (prm.u_vec == 2) {  // four reduction rows of one column
+          uint32_t* dst = Us + buf * BK * US + (f & 3) * 4 * US + (f >> 2);
+          dst[0] = wu.x; dst[US] = wu.y; dst[2 * US] = wu.z; dst[3 * US] = wu.w;
+        } else {               // four columns of one reduction row
+          *reinterpret_cast<uint4*>(Us + buf * BK * US + (f >> 4) * US + (f & 15) * 4) = wu;
+        }
+      }
+    } else {
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
       const int kl = u_kmajor ? (e & (BK - 1)) : (e >> 6);
       const int ql = u_kmajor ? (e >> 4) : (e & 63);
       Us[buf * BK * US + kl * US + ql] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
-      if (HAZARD_CHECK) hz |= hazard_bits(__float_as_uint(uraw[j]), true);
+    }
+    }
+    if (HAZARD_CHECK) {
+#pragma unroll
+      for (int j = 0; j < NU; ++j) hz |= hazard_bits(__float_as_uint(uraw[j]), true);
     }
     if (HAZARD_CHECK) {
       hz = __reduce_or_sync(0xffffffffu, hz);
