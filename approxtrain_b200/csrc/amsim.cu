@@ -466,6 +466,7 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
     }
   }
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
+  p.u_vec = aligned16(p.U) && p.u_sq == 1 && p.u_sk % 4 == 0 && p.Q % 4 == 0 && !getenv("AMSIM_NO_UVEC");
 #define AMSIM_GO(EX_, VEC_, LM_) return launch_fgrad_t<EX_, VEC_, LM_>(st, p, device)
 #define AMSIM_GO_LM(LM_)                                                                        \
   do {                                                                                          \

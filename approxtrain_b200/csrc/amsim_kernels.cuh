@@ -833,11 +833,22 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
       }
       vraw[i] = val;
     }
+    if (prm.u_vec) {  // q contiguous, rows and base 16-byte aligned, Q a multiple of 4 (checked by the host)
+#pragma unroll
+      for (int j = 0; j < NU / 4; ++j) {
+        const int f = j * NT + t;
+        const int pix = kbeg + kb * BK + (f >> 4), qg = q0 + (f & 15) * 4;
+        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (pix < kend && qg < prm.Q) val = __ldg(reinterpret_cast<const float4*>(Ug + (long long)pix * prm.u_sk + qg));
+        uraw[4 * j] = val.x; uraw[4 * j + 1] = val.y; uraw[4 * j + 2] = val.z; uraw[4 * j + 3] = val.w;
+      }
+    } else {
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
       const int pix = kbeg + kb * BK + (e >> 6), qg = q0 + (e & 63);
       uraw[j] = (pix < kend && qg < prm.Q) ? __ldg(Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq) : 0.f;
+    }
     }
   };
 
@@ -857,11 +868,27 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
         hz |= hazard_bits(__float_as_uint(f.x), false) | hazard_bits(__float_as_uint(f.y), false) |
               hazard_bits(__float_as_uint(f.z), false) | hazard_bits(__float_as_uint(f.w), false);
     }
+    if (prm.u_vec) {
+#pragma unroll
+      for (int j = 0; j < NU / 4; ++j) {
+        const int f = j * NT + t;
+        uint4 wu;
+        wu.x = enc_u<LM>(__float_as_uint(uraw[4 * j]), prm.m);
+        wu.y = enc_u<LM>(__float_as_uint(uraw[4 * j + 1]), prm.m);
+        wu.z = enc_u<LM>(__float_as_uint(uraw[4 * j + 2]), prm.m);
+        wu.w = enc_u<LM>(__float_as_uint(uraw[4 * j + 3]), prm.m);
+        *reinterpret_cast<uint4*>(Us + buf * BK * US + (f >> 4) * US + (f & 15) * 4) = wu;
+      }
+    } else {
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
       Us[buf * BK * US + (e >> 6) * US + (e & 63)] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
-      if (HAZARD_CHECK) hz |= hazard_bits(__float_as_uint(uraw[j]), true);
+    }
+    }
+    if (HAZARD_CHECK) {
+#pragma unroll
+      for (int j = 0; j < NU; ++j) hz |= hazard_bits(__float_as_uint(uraw[j]), true);
     }
     if (HAZARD_CHECK) {
       hz = __reduce_or_sync(0xffffffffu, hz);
