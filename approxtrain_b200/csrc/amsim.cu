@@ -655,6 +655,8 @@ int amsim_conv2d_geometry(int in_h, int in_w, int f_h, int f_w, int stride_h, in
   return AMSIM_OK;
 }
 
+static void dense_gather(Gather& g, int width);
+
 static int conv2d_fwd_impl(void* stream, const amsim_lut* lut, const float* x, const float* w, const float* scale,
                            const float* bias, float* y, int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
                            int out_w, int stride_h, int stride_w, int pad_top, int pad_left, int act, unsigned flags) {
@@ -673,6 +675,9 @@ static int conv2d_fwd_impl(void* stream, const amsim_lut* lut, const float* x, c
   g.PH = out_h; g.PW = out_w; g.ps_h = stride_h; g.ps_w = stride_w; g.off_t = pad_top; g.off_l = pad_left;
   g.lim_h = in_h; g.lim_w = in_w; g.dil_h = 1; g.dil_w = 1; g.SH = in_h; g.SW = in_w; g.SC = in_c; g.KW = f_w;
   fill_gather_divs(g);
+  if (f_h == 1 && f_w == 1 && stride_h == 1 && stride_w == 1 && pad_top == 0 && pad_left == 0 && out_h == in_h &&
+      out_w == in_w)
+    dense_gather(g, in_c);  // a plain GEMM over the pixels: no pixel -> (image, row, column) arithmetic
   p.u_t0 = 0; p.u_tj = f_w; p.u_ti = 1; p.u_tap = (long long)in_c * out_c; p.u_sk = out_c; p.u_sq = 1;
   p.o_sp = out_c; p.o_sq = 1;
   fill_lut(p, lut, /*v_is_first_operand=*/true);
@@ -737,6 +742,8 @@ int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, c
     g.PH = in_h; g.PW = in_w; g.ps_h = 1; g.ps_w = 1; g.off_t = bpt; g.off_l = bpl;
     g.lim_h = hole_h; g.lim_w = hole_w; g.dil_h = stride_h; g.dil_w = stride_w; g.KW = f_w;
     fill_gather_divs(g);
+    if (f_h == 1 && f_w == 1 && stride_h == 1 && stride_w == 1 && bpt == 0 && bpl == 0 && out_h == in_h && out_w == in_w)
+      dense_gather(g, out_c);  // a plain GEMM over the pixels
     // flipped filter with in/out channels swapped
     p.u_t0 = f_h * f_w - 1; p.u_tj = -f_w; p.u_ti = -1;
     if (i32) return launch_naive_i32((cudaStream_t)stream, p, lut, false);
@@ -831,10 +838,11 @@ int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, 
   }
   if (!x || !dy) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   if (f_h == 1 && f_w == 1 && stride_h == 1 && stride_w == 1 && pad_top == 0 && pad_left == 0 && out_h == in_h &&
-      out_w == in_w && !(flags & AMSIM_INT32) && wgrad_swap(in_c, out_c)) {
+      out_w == in_w && !(flags & AMSIM_INT32)) {
     // 1x1, stride 1, no padding: dw[c,k] = sum_pixels AM(x[pix,c], dy[pix,k]) is a plain GEMM
+    // (no pixel -> (image, row, column) arithmetic in the gather, and either operand role)
     Params q{};
-    setup_wgrad(q, lut, x, dy, dw, npix, in_c, out_c, /*swap=*/true);
+    setup_wgrad(q, lut, x, dy, dw, npix, in_c, out_c, wgrad_swap(in_c, out_c));
     return launch_fgrad((cudaStream_t)stream, q, flags & AMSIM_DETERMINISTIC, workspace, workspace_bytes, lut->device);
   }
   Params p{};
