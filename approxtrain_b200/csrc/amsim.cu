@@ -286,7 +286,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
       const size_t slot_bytes = (size_t)grid * 2 * TR * TC * L::NT * sizeof(float);
       const size_t bytes = slot_bytes + (size_t)ctas * sizeof(int);
       rc = scratch_alloc(st, device, bytes, &p.ws);
-      if (rc) return rc;
+      if (rc == AMSIM_OK) {
       p.sk_count = reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) + slot_bytes);
       cudaError_t e1 = cudaMemsetAsync(p.sk_count, 0, (size_t)ctas * sizeof(int), st);
       if (e1 == cudaSuccess) {
@@ -300,6 +300,10 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
       CUDA_TRY(e1);
       CUDA_TRY(e2);
       return AMSIM_OK;
+      }
+      // no scratch to be had (pool exhausted, allocator unsupported): the plain grid needs none
+      (void)cudaGetLastError();
+      p.ws = nullptr;
     }
   }
 
