@@ -64,6 +64,7 @@ struct amsim_lut {
   int enc_bytes = 0;           // size of each encoded copy, multiple of 16
   bool additive = false;       // encoded entry(i, j) == i + j for every pair: no lookups needed
   int direct = 0;              // LM_DIRECT_MBM / LM_DIRECT_MIT: no table at all, m = 23
+  bool wide = false;           // 16-bit entries (d_raw / d_raw_t hold uint16), looked up in global memory
 };
 
 namespace {
@@ -89,6 +90,35 @@ int parse_mant_width(const char* path) {
 // number so that  entry << (23 - m)  is exactly what AMsimulator.inl:22-23,31-32
 // add to the exponent/mantissa bits.
 inline uint8_t encode_entry(uint8_t v, int m) { return (uint8_t)(((v >> 7) << m) + (v & 0x7f)); }
+
+// 16-bit entries: both orientations as uint16 tables in global memory.
+int upload_lut16(const uint16_t* entries, int m, int device, amsim_lut** out) {
+  int prev = 0;
+  CUDA_TRY(cudaGetDevice(&prev));
+  CUDA_TRY(cudaSetDevice(device));
+  amsim_lut* h = new amsim_lut();
+  h->m = m;
+  h->device = device;
+  h->refs = 1;
+  h->wide = true;
+  const size_t side = (size_t)1 << m, n = side * side;
+  std::vector<uint16_t> tr(n);
+  for (size_t a = 0; a < side; ++a)
+    for (size_t b = 0; b < side; ++b) tr[b * side + a] = entries[a * side + b];
+  cudaError_t e = cudaMalloc(&h->d_raw, n * 2);
+  if (e == cudaSuccess) e = cudaMalloc(&h->d_raw_t, n * 2);
+  if (e == cudaSuccess) e = cudaMemcpy(h->d_raw, entries, n * 2, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(h->d_raw_t, tr.data(), n * 2, cudaMemcpyHostToDevice);
+  cudaSetDevice(prev);
+  if (e != cudaSuccess) {
+    cudaFree(h->d_raw_t);
+    cudaFree(h->d_raw);
+    delete h;
+    return fail(AMSIM_ERR_CUDA, "upload of 16-bit lut: %s", cudaGetErrorString(e));
+  }
+  *out = h;
+  return AMSIM_OK;
+}
 
 int upload_lut(const uint8_t* bytes, int m, int device, amsim_lut** out) {
   int prev = 0;
@@ -187,7 +217,9 @@ void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
   p.rmask = ((1u << lut->m) - 1u) << lut->m;
   p.cmask = (1u << lut->m) - 1u;
   p.cadj = (1u << 23) - 128u * p.mult;
-  p.lut_mode = lut->direct ? lut->direct : lut->m > 7 ? LM_GLOBAL : (lut->additive ? LM_ADD : LM_SMEM);
+  p.lut_mode = lut->direct ? lut->direct
+               : lut->wide ? LM_GLOBAL16
+               : lut->m > 7 ? LM_GLOBAL : (lut->additive ? LM_ADD : LM_SMEM);
   p.lut_raw = v_is_first_operand ? lut->d_raw_t : lut->d_raw;
   p.v_first = v_is_first_operand ? 1 : 0;
   p.exact_only = getenv("AMSIM_EXACT_ONLY") != nullptr;
@@ -261,7 +293,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   // being captured into a graph (the scratch comes from the stream-ordered allocator).
   // (not for tables in global memory: those launches are bound by L2 gathers, and lock-step CTAs
   // measured 50 % slower there)
-  if constexpr (!EXACT && LM != LM_GLOBAL) {
+  if constexpr (!EXACT && !lm_global(LM)) {
     int rc = ensure_smem(gather_gemm<1, EXACT, VEC, GM_BALANCED, LM>, smem_plain, device);
     if (rc) return rc;
     int slots = 0;
@@ -310,7 +342,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   // Fast mode, small launches inside a graph capture: a thread-block cluster of `ksplit` CTAs
   // shares each tile's reduction when the tiles alone cannot fill the resident CTA slots.
   int ksplit = 1;
-  if (!EXACT && LM != LM_GLOBAL) {
+  if (!EXACT && !lm_global(LM)) {
     const int slots = 148 * AMSIM_CTAS1;
     while (ksplit < 8 && ctas * (ksplit * 2) <= slots && nkb / (ksplit * 2) >= 6) ksplit *= 2;
     if (const char* f = getenv("AMSIM_FORCE_KSPLIT")) ksplit = atoi(f) > 0 ? atoi(f) : 1;
@@ -326,7 +358,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
     CUDA_TRY(cudaGetLastError());
     return AMSIM_OK;
   }
-  constexpr int kClusterMode = (!EXACT && LM != LM_GLOBAL) ? GM_CLUSTER : GM_PLAIN;
+  constexpr int kClusterMode = (!EXACT && !lm_global(LM)) ? GM_CLUSTER : GM_PLAIN;
   int rc = ensure_smem(gather_gemm<1, EXACT, VEC, kClusterMode, LM>, smem, device);
   if (rc) return rc;
   cudaLaunchConfig_t cfg;
@@ -369,6 +401,7 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
   if (p.lut_mode == LM_DIRECT_MIT) { if (vec) AMSIM_GO(true, true, LM_DIRECT_MIT); else AMSIM_GO(true, false, LM_DIRECT_MIT); }
   if (p.lut_mode == LM_ADD) AMSIM_GO_LM(LM_ADD);
   if (p.lut_mode == LM_GLOBAL) AMSIM_GO_LM(LM_GLOBAL);
+  if (p.lut_mode == LM_GLOBAL16) AMSIM_GO_LM(LM_GLOBAL16);
   AMSIM_GO_LM(LM_SMEM);
 #undef AMSIM_GO_LM
 #undef AMSIM_GO
@@ -466,6 +499,7 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
       if (p.lut_mode == LM_DIRECT_MIT) return launch_fgrad_thin<LM_DIRECT_MIT>(st, p, tq, device);
       if (p.lut_mode == LM_ADD) return launch_fgrad_thin<LM_ADD>(st, p, tq, device);
       if (p.lut_mode == LM_GLOBAL) return launch_fgrad_thin<LM_GLOBAL>(st, p, tq, device);
+      if (p.lut_mode == LM_GLOBAL16) return launch_fgrad_thin<LM_GLOBAL16>(st, p, tq, device);
       return launch_fgrad_thin<LM_SMEM>(st, p, tq, device);
     }
   }
@@ -481,6 +515,7 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   if (p.lut_mode == LM_DIRECT_MIT) { if (vec) AMSIM_GO(true, true, LM_DIRECT_MIT); else AMSIM_GO(true, false, LM_DIRECT_MIT); }
   if (p.lut_mode == LM_ADD) AMSIM_GO_LM(LM_ADD);
   if (p.lut_mode == LM_GLOBAL) AMSIM_GO_LM(LM_GLOBAL);
+  if (p.lut_mode == LM_GLOBAL16) AMSIM_GO_LM(LM_GLOBAL16);
   AMSIM_GO_LM(LM_SMEM);
 #undef AMSIM_GO_LM
 #undef AMSIM_GO
@@ -490,6 +525,7 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
 int launch_naive_i32(cudaStream_t st, Params& p, const amsim_lut* lut, bool fgrad) {
   if (p.P <= 0 || p.Q <= 0) return AMSIM_OK;
   if (lut->direct) return fail(AMSIM_ERR_UNSUPPORTED, "the direct 32-bit models are FP32 only");
+  if (lut->wide) return fail(AMSIM_ERR_UNSUPPORTED, "tables of 16-bit entries are FP32 only");
   p.lut_raw = lut->d_raw;  // rows by the first operand; v_first tells the kernel which operand that is
   const long long n = (long long)p.P * p.Q;
   const unsigned blocks = (unsigned)((n + 127) / 128);
@@ -577,14 +613,22 @@ int amsim_lut_open(const char* path, int device, amsim_lut** out) {
   FILE* f = fopen(real, "rb");
   if (!f) return fail(AMSIM_ERR_LUT_IO, "lut file '%s' cannot be opened", path);
   const size_t want = (size_t)1 << (2 * m);
-  std::vector<uint8_t> buf(want + 1);
-  const size_t got = fread(buf.data(), 1, want + 1, f);
+  std::vector<uint8_t> buf(2 * want + 2);
+  const size_t got = fread(buf.data(), 1, 2 * want + 1, f);
   fclose(f);
-  if (got != want)
-    return fail(AMSIM_ERR_LUT_SIZE, "lut file '%s' holds %s%zu bytes, m = %d needs exactly %zu", path,
-                got > want ? "more than " : "", got > want ? want : got, m, want);
+  // exactly 2^(2m) bytes: the reference's format; exactly twice that: 16-bit little-endian entries
+  if (got != want && got != 2 * want)
+    return fail(AMSIM_ERR_LUT_SIZE, "lut file '%s' holds %s%zu bytes, m = %d needs exactly %zu (or %zu for 16-bit entries)",
+                path, got > 2 * want ? "more than " : "", got > 2 * want ? 2 * want : got, m, want, 2 * want);
   amsim_lut* h = nullptr;
-  const int rc = upload_lut(buf.data(), m, device, &h);
+  int rc;
+  if (got == 2 * want) {
+    std::vector<uint16_t> wide(want);
+    for (size_t i = 0; i < want; ++i) wide[i] = (uint16_t)(buf[2 * i] | (buf[2 * i + 1] << 8));
+    rc = upload_lut16(wide.data(), m, device, &h);
+  } else {
+    rc = upload_lut(buf.data(), m, device, &h);
+  }
   if (rc) return rc;
   h->key = key;
   g_lut_cache[key] = h;
@@ -628,7 +672,7 @@ int amsim_mul(void* stream, const amsim_lut* lut, const float* a, const float* b
   size_t blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   AMSIM_COUNT_LAUNCH();
-  mul_elementwise<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, lut->d_raw, lut->m, lut->direct);
+  mul_elementwise<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, lut->d_raw, lut->m, lut->direct ? lut->direct : lut->wide ? LM_GLOBAL16 : 0);
   CUDA_TRY(cudaGetLastError());
   return AMSIM_OK;
 }

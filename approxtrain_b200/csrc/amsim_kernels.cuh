@@ -177,6 +177,19 @@ constexpr int LM_ADD = 2;     // additive table, entry(i, j) == i + j for every 
                               // multipliers): the lookup is an integer add of the operands' mantissa
                               // fields, no table access at all; detected when the LUT is opened
 
+constexpr int LM_GLOBAL16 = 5;  // table of 16-bit entries in global memory (carry << 15 | top 15 mantissa bits)
+__host__ __device__ constexpr bool lm_global(int lm) { return lm == LM_GLOBAL || lm == LM_GLOBAL16; }
+// Table term of one product from a table in global memory: (carry << 23) + mantissa bits.
+template <int LM>
+__device__ __forceinline__ uint32_t global_entry(const uint8_t* __restrict__ lut_g, uint32_t idx, uint32_t mult,
+                                                 uint32_t cadj) {
+  if (LM == LM_GLOBAL16) {
+    const uint32_t v = __ldg(reinterpret_cast<const uint16_t*>(lut_g) + idx);
+    return ((v & 0x7FFFu) << 8) + ((v >> 15) << 23);
+  }
+  const uint32_t v = __ldg(lut_g + idx);
+  return v * mult + (v >> 7) * cadj;
+}
 constexpr int LM_DIRECT_MBM = 3;  // no table: the 32-bit minimally-biased model computed per product
 constexpr int LM_DIRECT_MIT = 4;  // no table: the 32-bit Mitchell model computed per product
 __host__ __device__ constexpr bool lm_direct(int lm) { return lm == LM_DIRECT_MBM || lm == LM_DIRECT_MIT; }
@@ -273,7 +286,7 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
   bool nz[TC];
 #pragma unroll
   for (int t = 0; t < TC; ++t) {
-    ci[t] = LM == LM_GLOBAL ? (w[t] & cmask) : ((w[t] & 0xFFu) | lut_base);
+    ci[t] = lm_global(LM) ? (w[t] & cmask) : ((w[t] & 0xFFu) | lut_base);
     nz[t] = NZEXP ? (w[t] & 0x7F800000u) != 0u : w[t] != 0u;
     if (EXACT) {
       // AMsimulator.inl:26-33: exponent sum - 127, folded into the lane word
@@ -303,9 +316,8 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
         uint32_t e;
         if (LM == LM_ADD) {
           e = du;  // entry(i, j) << (23 - m) == (i << (23 - m)) + (j << (23 - m)); the j term is in cs
-        } else if (LM == LM_GLOBAL) {
-          const uint32_t v = __ldg(lut_g + ((uu[r] & rmask) | ci[t]));
-          e = v * mult + (v >> 7) * cadj;
+        } else if (lm_global(LM)) {
+          e = global_entry<LM>(lut_g, (uu[r] & rmask) | ci[t], mult, cadj);
         } else {
           e = lds_u8((uu[r] & rmask) | ci[t]) * mult;
         }
@@ -1056,7 +1068,7 @@ __global__ void __launch_bounds__(128) fgrad_exact_thin(const Params prm) {
     for (int kk = 0; kk < BK; ++kk) {
       const uint32_t wv = vs[kk * BPT];
       // same arithmetic as the deterministic branch of mac_step
-      const uint32_t ci = LM == LM_GLOBAL ? (wv & prm.cmask) : ((wv & 0xFFu) | lut_base);
+      const uint32_t ci = lm_global(LM) ? (wv & prm.cmask) : ((wv & 0xFFu) | lut_base);
       const uint32_t cs = (LM == LM_ADD ? wv : (wv & 0xFF800000u)) - 0x3F800000u;
       const int cn = (int)(0x3F800000u - (wv & 0x7F800000u));
 #pragma unroll
@@ -1071,9 +1083,8 @@ __global__ void __launch_bounds__(128) fgrad_exact_thin(const Params prm) {
         uint32_t e;
         if (LM == LM_ADD) {
           e = uu & 0x007FFFFFu;
-        } else if (LM == LM_GLOBAL) {
-          const uint32_t v = __ldg(prm.lut_raw + ((uu & prm.rmask) | ci));
-          e = v * prm.mult + (v >> 7) * prm.cadj;
+        } else if (lm_global(LM)) {
+          e = global_entry<LM>(prm.lut_raw, (uu & prm.rmask) | ci, prm.mult, prm.cadj);
         } else {
           e = lds_u8((uu & prm.rmask) | ci) * prm.mult;
         }
@@ -1106,12 +1117,18 @@ __global__ void reduce_splits(const float* __restrict__ ws, float* __restrict__ 
 }
 
 // The reference primitive on raw LUT bytes (cuda/AMsimulator.inl:13-36).
-__device__ __forceinline__ uint32_t am_mul_bits(uint32_t at, uint32_t bt, const uint8_t* __restrict__ lut, int m) {
+// `wide`: 16-bit entries (carry << 15 | top 15 mantissa bits of the product), a format extension.
+__device__ __forceinline__ uint32_t am_mul_bits(uint32_t at, uint32_t bt, const uint8_t* __restrict__ lut, int m,
+                                                bool wide = false) {
   const uint32_t mask = ((1u << m) - 1u) << (23 - m);
   const uint32_t idx = ((at & mask) >> (23 - 2 * m)) | ((bt & mask) >> (23 - m));
-  const uint32_t v = __ldg(lut + idx);
   const uint32_t e = ((at >> 23) & 0xFFu) + ((bt >> 23) & 0xFFu);
   if (e <= 127u) return 0u;
+  if (wide) {
+    const uint32_t v = __ldg(reinterpret_cast<const uint16_t*>(lut) + idx);
+    return ((at ^ bt) & 0x80000000u) + ((e - 127u + (v >> 15)) << 23) + ((v & 0x7FFFu) << 8);
+  }
+  const uint32_t v = __ldg(lut + idx);
   return ((at ^ bt) & 0x80000000u) + ((e - 127u + (v >> 7)) << 23) + ((v & 0x7Fu) << (23 - m));
 }
 
@@ -1191,7 +1208,7 @@ __global__ void mul_elementwise(const float* __restrict__ a, const float* __rest
     uint32_t r;
     if (lut_mode == LM_DIRECT_MBM) r = direct_mul_bits<true>(at, bt);
     else if (lut_mode == LM_DIRECT_MIT) r = direct_mul_bits<false>(at, bt);
-    else r = am_mul_bits(at, bt, lut, m);
+    else r = am_mul_bits(at, bt, lut, m, lut_mode == LM_GLOBAL16);
     out[i] = __uint_as_float(r);
   }
 }

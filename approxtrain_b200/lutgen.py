@@ -24,16 +24,28 @@ from typing import Callable
 import numpy as np
 
 
-def generate(model: Callable[[np.ndarray, np.ndarray], np.ndarray], m: int) -> np.ndarray:
-    """Return the 2^(2m) LUT bytes for ``model`` (vectorised: float32 arrays in, float32 array out)."""
+def generate(model: Callable[[np.ndarray, np.ndarray], np.ndarray], m: int, entry_bits: int = 8) -> np.ndarray:
+    """Return the 2^(2m) LUT entries for ``model`` (vectorised: float32 arrays in, float32 array out).
+
+    ``entry_bits=8`` is the reference's format (uint8 array).  ``entry_bits=16`` is a format
+    extension of this library (little-endian uint16 array, written to a file of twice the
+    size under the same ``<MODEL>_<m>.bin`` name): ``carry << 15 | top 15 mantissa bits`` of
+    the product.  A byte keeps 7 mantissa bits, so tables for m = 8..11 in the reference's
+    format drop the product's leading mantissa bits; 16-bit entries keep them."""
     if not 1 <= m <= 11:
         raise ValueError("mantissa width must be in 1..11 (the ops derive a_shift = 23 - 2m)")
+    if entry_bits not in (8, 16):
+        raise ValueError("entry_bits must be 8 or 16")
     n = 1 << m
     i, j = np.meshgrid(np.arange(n, dtype=np.uint32), np.arange(n, dtype=np.uint32), indexing="ij")
     one = np.uint32(0x3F800000)
     a = (one | (i << np.uint32(23 - m))).view(np.float32)
     b = (one | (j << np.uint32(23 - m))).view(np.float32)
     c = np.ascontiguousarray(model(a.reshape(-1), b.reshape(-1)), dtype=np.float32).view(np.uint32)
+    if entry_bits == 16:
+        mant = ((c >> np.uint32(8)) & np.uint32(0x7FFF)).astype(np.uint16)
+        carry = np.where((c & np.uint32(0x7F800000)) > one, 0x8000, 0).astype(np.uint16)
+        return (carry | mant).astype("<u2")
     mask = np.uint32(((1 << m) - 1) << (23 - m))
     mant = ((c & mask) >> np.uint32(23 - m)).astype(np.uint8)          # truncation to uint8 as in lut_gen.cc:114
     carry = np.where((c & np.uint32(0x7F800000)) > one, 0x80, 0).astype(np.uint8)
@@ -54,13 +66,13 @@ def c_model(library: str, symbol: str) -> Callable[[np.ndarray, np.ndarray], np.
     return model
 
 
-def write(path: str, model: Callable, m: int) -> None:
+def write(path: str, model: Callable, m: int, entry_bits: int = 8) -> None:
     import os
     import re
     mm = re.search(r"_(\d+)\.[^._/]*$", os.path.basename(path))
     if not mm or int(mm.group(1)) != m:
         raise ValueError(f"{path!r}: the ops read the mantissa width from the file name, it must end in _{m}.<ext>")
-    generate(model, m).tofile(path)
+    generate(model, m, entry_bits).tofile(path)
 
 
 if __name__ == "__main__":

@@ -88,6 +88,13 @@ const char* amsim_version(void);
  * the kernels add the operands' mantissa fields instead, with identical bits
  * (set AMSIM_NO_ADDITIVE in the environment before opening to force the table).
  *
+ * Format extension (no reference counterpart): a file of exactly 2 * 2^(2m) bytes
+ * under the same name holds 16-bit little-endian entries, carry << 15 | top 15
+ * mantissa bits of the product.  A byte keeps 7 mantissa bits, so byte tables for
+ * m = 8..11 drop the product's leading bits; 16-bit entries keep them
+ * (approxtrain_b200/lutgen.py writes both formats).  Looked up in global memory,
+ * FP32 ops only; amsim_lut_info reports the same m, mask and shifts.
+ *
  * Two pseudo-paths select the reference's direct C simulation of its 32-bit
  * multipliers (mantissa width 23, README.md:107: "for multipliers with mantissa
  * bit-width greater or equal to 12, direct C simulation should be used"):

@@ -121,6 +121,18 @@ static uint32_t direct_mul_bits(uint32_t at, uint32_t bt, int mbm) {
 uint32_t am_mul_bits(uint32_t at, uint32_t bt, const uint8_t* lut, int m) {
   if (m == AM_DIRECT_MBM32) return direct_mul_bits(at, bt, 1);
   if (m == AM_DIRECT_MIT32) return direct_mul_bits(at, bt, 0);
+  if (m & AM_WIDE_ENTRIES) {
+    /* Format extension (no reference counterpart): 16-bit little-endian entries,
+     * carry << 15 | top 15 mantissa bits of the product; everything else as below. */
+    const int mw = m & ~AM_WIDE_ENTRIES;
+    const uint32_t mask16 = ((1u << mw) - 1u) << (23 - mw);
+    const uint32_t idx16 = ((at & mask16) >> (23 - 2 * mw)) | ((bt & mask16) >> (23 - mw));
+    const uint32_t v16 = (uint32_t)lut[2 * (size_t)idx16] | ((uint32_t)lut[2 * (size_t)idx16 + 1] << 8);
+    uint32_t e16 = ((at & 0x7f800000u) >> 23) + ((bt & 0x7f800000u) >> 23);
+    if (e16 <= 127u) return 0u;
+    e16 = e16 - 127u + (v16 >> 15);
+    return ((at ^ bt) & 0x80000000u) + (e16 << 23) + ((v16 & 0x7fffu) << 8);
+  }
   const uint32_t mant_mask = ((1u << m) - 1u) << (23 - m);
   const uint32_t a_shift = (uint32_t)(23 - 2 * m);
   const uint32_t b_shift = (uint32_t)(23 - m);

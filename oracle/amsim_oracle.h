@@ -43,6 +43,10 @@ int am_load_lut(const char* path, uint8_t** out, int* m);
  * (cuda/FPmultMBM_fast32.inl:41-126, cuda/Mitchell_32.inl; lut may be NULL). */
 #define AM_DIRECT_MBM32 132
 #define AM_DIRECT_MIT32 123
+/* m | AM_WIDE_ENTRIES: the table holds 2^(2m) 16-bit little-endian entries
+ * (carry << 15 | top 15 mantissa bits) instead of bytes: a format extension of this
+ * repository that makes m = 8..11 numerically meaningful; no reference counterpart. */
+#define AM_WIDE_ENTRIES 0x100
 
 /* cuda/AMsimulator.inl:13-36 on raw bit patterns. */
 uint32_t am_mul_bits(uint32_t at, uint32_t bt, const uint8_t* lut, int m);

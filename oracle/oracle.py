@@ -24,6 +24,7 @@ _REF_LIB = os.path.join(_HERE, "_ref", "libref_amsim.so")
 DIRECT_MBM32 = 132
 DIRECT_MIT32 = 123
 NO_LUT = np.zeros(1, dtype=np.uint8)
+WIDE_ENTRIES = 0x100   # m | WIDE_ENTRIES: the table holds 16-bit little-endian entries (pass the bytes)
 
 _f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 _u32p = np.ctypeslib.ndpointer(dtype=np.uint32, flags="C_CONTIGUOUS")
@@ -69,6 +70,8 @@ def load_lut(path: str):
     if m < 0:
         raise ValueError(f"cannot parse mantissa width from {path!r}")
     data = np.fromfile(path, dtype=np.uint8)
+    if data.size == 2 << (2 * m):      # 16-bit entries (format extension)
+        return data, m | WIDE_ENTRIES
     if data.size != 1 << (2 * m):
         raise ValueError(f"{path}: {data.size} bytes, expected {1 << (2 * m)}")
     return data, m

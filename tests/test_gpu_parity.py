@@ -905,3 +905,45 @@ def test_deterministic_mode_hazard_stages(ops, oracle, luts, exact_only, monkeyp
                 same(ops.convam(dev(xs), dev(ws), **kw_), want_y, f"{name} fwd v{variant}")
                 same(ops.convam_input_grad(xs.shape, dev(ws), dev(ds), **kw_), want_dx, f"{name} input-grad v{variant}")
                 same(ops.convam_filter_grad(ws.shape, dev(xs), dev(ds), **kw_), want_dw, f"{name} filter-grad v{variant}")
+
+
+@pytest.mark.parametrize("m", [5, 9])
+def test_tables_with_16_bit_entries(ops, oracle, m, tmp_path):
+    """A LUT file of twice the usual size holds 16-bit entries (carry << 15 | 15 mantissa
+    bits), a format extension that makes m = 8..11 numerically meaningful.  The table is
+    looked up in global memory; primitive bit-exact for every exponent class, GEMM ops
+    bit-exact in deterministic mode and within the bar in fast mode."""
+    from approxtrain_b200 import lutgen
+    from oracle.oracle import DIRECT_MBM32, NO_LUT, load_lut
+    path = str(tmp_path / f"MBMW_{m}.bin")
+    lutgen.write(path, lambda a, b: oracle.mul(a, b, NO_LUT, DIRECT_MBM32), m, entry_bits=16)
+    lut, mw = load_lut(path)
+    kat = np.load(os.path.join(GOLDEN, "prim_kat.npz"))      # operand grid over all exponent classes
+    at, bt = kat["at"], kat["bt"]
+    got = ops.am_multiply(dev(at.view(np.float32)), dev(bt.view(np.float32)), path).cpu().numpy().view(np.uint32)
+    want = oracle.mul(at.view(np.float32), bt.view(np.float32), lut, mw).view(np.uint32)
+    assert np.array_equal(got, want)
+    rng = np.random.default_rng(160 + m)
+    for (n, h, w, c, kh, kw, k, s, pad) in [(2, 9, 9, 8, 3, 3, 20, 1, "SAME"), (1, 12, 12, 3, 5, 5, 6, 2, "VALID")]:
+        x, wt = _conv_case(rng, n, h, w, c, kh, kw, k)
+        g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+        dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+        kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=path)
+        want_y, want_dx = oracle.conv2d_fwd(g, x, wt, lut, mw), oracle.conv2d_bwd_input(g, wt, dy, lut, mw)
+        want_dw = oracle.conv2d_bwd_filter(g, x, dy, lut, mw)
+        assert_bit_equal(ops.convam(dev(x), dev(wt), deterministic=True, **kw_).cpu().numpy(), want_y, "wide fwd det")
+        assert_bit_equal(ops.convam_input_grad(x.shape, dev(wt), dev(dy), deterministic=True, **kw_).cpu().numpy(), want_dx, "wide dx det")
+        assert_bit_equal(ops.convam_filter_grad(wt.shape, dev(x), dev(dy), deterministic=True, **kw_).cpu().numpy(), want_dw, "wide dw det")
+        assert_close(ops.convam(dev(x), dev(wt), **kw_).cpu().numpy(), want_y, "wide fwd fast")
+        assert_close(ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_).cpu().numpy(), want_dx, "wide dx fast")
+        assert_close(ops.convam_filter_grad(wt.shape, dev(x), dev(dy), **kw_).cpu().numpy(), want_dw, "wide dw fast")
+    a = rng.standard_normal((3, 10, 21)).astype(np.float32)
+    b = rng.standard_normal((3, 21, 14)).astype(np.float32)
+    assert_bit_equal(ops.matmulam(dev(a), dev(b), mant_mul_lut=path, deterministic=True).cpu().numpy(),
+                     oracle.matmul(a, b, lut, mw), "wide matmul")
+    with pytest.raises(Exception):   # int32 ops take byte tables only
+        ops.denseam(dev(np.ones((2, 3), np.int32)), dev(np.ones((3, 2), np.int32)), path)
+    bad = str(tmp_path / "BAD_5.bin")
+    np.zeros(3 << 10, np.uint8).tofile(bad)     # neither 2^(2m) nor twice that
+    with pytest.raises(Exception):
+        ops.am_multiply(dev(a), dev(a), bad)
