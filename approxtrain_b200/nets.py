@@ -1,4 +1,4 @@
-"""The five networks BASELINE.json's configs name, built from the AM layers.
+"""The five benchmark networks (LeNet-300-100, LeNet-5, the conv microbenchmark's layers, ResNet-50, Transformer), built from the AM layers.
 
 Every convolution is ``AMConv2D``, every dense layer ``denseam``, every attention
 product ``MatMulAM``; pooling, normalisation, activations, softmax and the loss

@@ -15,7 +15,7 @@ def beq(a, b):
 
 
 def test_lenet300100_step_against_oracle(oracle, luts):
-    """BASELINE config 1: 784-300-100-10, batch 256, x ~ U[0,1), MBM_7, one
+    """Benchmark configuration 1 (LeNet-300-100): 784-300-100-10, batch 256, x ~ U[0,1), MBM_7, one
     forward + backward + SGD step.  Logits are bit-exact vs the oracle; each
     layer's gradients are bit-exact given the upstream gradient torch produced."""
     from approxtrain_b200.nets import LeNet300100
@@ -124,7 +124,7 @@ def test_matmul_gradient_wiring_with_transposes_and_alpha(oracle, luts, ta, tb):
 
 
 def test_lenet5_trains_on_a_fixed_batch():
-    """BASELINE config 2 shapes: batch 128 of 28x28x1, MIT_7, He-normal."""
+    """Benchmark configuration 2 (LeNet-5) shapes: batch 128 of 28x28x1, MIT_7, He-normal."""
     from approxtrain_b200.nets import LeNet5
     from approxtrain_b200.dp import DataParallelSGD
     torch.manual_seed(0)

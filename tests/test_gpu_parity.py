@@ -362,7 +362,7 @@ def test_errors_through_the_abi(ops):
 
 
 def test_full_size_properties_config3_shapeB(ops):
-    """BASELINE config-3 shape B (N64 14x14 256->256, 3x3 SAME) at full size,
+    """Conv microbenchmark shape B (N64 14x14 256->256, 3x3 SAME) at full size,
     checked through properties that need no oracle run:
     linearity in the power-of-two scaling of an operand (exact for the AM
     multiplier: only exponents change) and <y,dy> = <dw,w>-style consistency is
