@@ -41,6 +41,10 @@ constexpr int BQ = 64;  // q extent of a CTA tile (4 warps x 16)
 constexpr int TR = 16;  // q values per warp, held as registers
 constexpr int TC = 4;   // consecutive p values per lane
 constexpr int US = BQ + 4;  // padded U row (words): 2-way instead of 16-way store conflicts for k-contiguous loads
+// One double-buffered U tile, in words.  Additive tables keep a second tile right behind the
+// first: sign+exponent words in the first, mantissa-field words in the second, so the inner
+// loop (pure arithmetic there, shared memory has room) does not unpack them per k-step.
+constexpr int U_TILE_WORDS = 2 * BK * US;
 
 #ifndef AMSIM_CTAS1
 #define AMSIM_CTAS1 3
@@ -301,11 +305,16 @@ __device__ __forceinline__ void mac_step(float (&acc)[TR][TC], const uint32_t* _
   for (int g4 = 0; g4 < TR / 4; ++g4) {
     const uint4 u4 = *reinterpret_cast<const uint4*>(urow + 4 * g4);
     const uint32_t uu[4] = {u4.x, u4.y, u4.z, u4.w};
+    uint32_t dd[4] = {0u, 0u, 0u, 0u};
+    if (LM == LM_ADD) {  // additive table: the uniform operand's mantissa fields, stored apart
+      const uint4 d4 = *reinterpret_cast<const uint4*>(urow + U_TILE_WORDS + 4 * g4);
+      dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
+    }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const uint32_t pp = uu[r] & 0xFF800000u;
+      const uint32_t pp = LM == LM_ADD ? uu[r] : (uu[r] & 0xFF800000u);
       const int ee = (int)(uu[r] & 0x7F800000u);
-      const uint32_t du = uu[r] & 0x007FFFFFu;  // additive table: the uniform operand's mantissa field
+      const uint32_t du = dd[r];
 #pragma unroll
       for (int t = 0; t < TC; ++t) {
         if (lm_direct(LM)) {  // both models are symmetric in their operands
@@ -352,13 +361,40 @@ __device__ __forceinline__ uint32_t enc_u(uint32_t bits, int m) {
   return (bits & 0xFF800000u) | (((bits >> (23 - m)) & ((1u << m) - 1u)) << m);
 }
 
+// Stores one encoded uniform-operand word (additive tables: its two halves in the two tiles).
+template <int LM>
+__device__ __forceinline__ void store_u(uint32_t* dst, uint32_t bits, int m) {
+  const uint32_t w = enc_u<LM>(bits, m);
+  if (LM == LM_ADD) {
+    dst[0] = w & 0xFF800000u;
+    dst[U_TILE_WORDS] = w & 0x007FFFFFu;
+  } else {
+    dst[0] = w;
+  }
+}
+template <int LM>
+__device__ __forceinline__ void store_u4(uint32_t* dst, const float (&f)[4], int m) {
+  uint4 w;
+  w.x = enc_u<LM>(__float_as_uint(f[0]), m);
+  w.y = enc_u<LM>(__float_as_uint(f[1]), m);
+  w.z = enc_u<LM>(__float_as_uint(f[2]), m);
+  w.w = enc_u<LM>(__float_as_uint(f[3]), m);
+  if (LM == LM_ADD) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w.x & 0xFF800000u, w.y & 0xFF800000u, w.z & 0xFF800000u, w.w & 0xFF800000u);
+    *reinterpret_cast<uint4*>(dst + U_TILE_WORDS) =
+        make_uint4(w.x & 0x007FFFFFu, w.y & 0x007FFFFFu, w.z & 0x007FFFFFu, w.w & 0x007FFFFFu);
+  } else {
+    *reinterpret_cast<uint4*>(dst) = w;
+  }
+}
+
 template <int WP>
 struct SmemLayout {
   static constexpr int NT = WP * 128;
   static constexpr int BP = WP * 128;
   static constexpr int VS = BP + 4;  // padded row: conflict-free 4-row scatter
   static constexpr int V_WORDS = 2 * BK * VS;
-  static constexpr int U_WORDS = 2 * BK * US;
+  static constexpr int U_WORDS = 2 * U_TILE_WORDS;  // the second tile is used by additive tables only
   static constexpr int FLAG_WORDS = 2 * 4 * WP;  // deterministic kernels: one hazard word per stage and warp
   static constexpr int TILE_BYTES = (V_WORDS + U_WORDS + FLAG_WORDS) * 4;
   // tiles, then the table at the next multiple of its alignment
@@ -610,16 +646,13 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 #pragma unroll
       for (int j = 0; j < NU / 4; ++j) {
         const int f = j * NT + t;
-        uint4 wu;
-        wu.x = enc_u<LM>(__float_as_uint(uraw[4 * j]), prm.m);
-        wu.y = enc_u<LM>(__float_as_uint(uraw[4 * j + 1]), prm.m);
-        wu.z = enc_u<LM>(__float_as_uint(uraw[4 * j + 2]), prm.m);
-        wu.w = enc_u<LM>(__float_as_uint(uraw[4 * j + 3]), prm.m);
         if (prm.u_vec == 2) {  // four reduction rows of one column
           uint32_t* dst = Us + buf * BK * US + (f & 3) * 4 * US + (f >> 2);
-          dst[0] = wu.x; dst[US] = wu.y; dst[2 * US] = wu.z; dst[3 * US] = wu.w;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) store_u<LM>(dst + i * US, __float_as_uint(uraw[4 * j + i]), prm.m);
         } else {               // four columns of one reduction row
-          *reinterpret_cast<uint4*>(Us + buf * BK * US + (f >> 4) * US + (f & 15) * 4) = wu;
+          const float f4[4] = {uraw[4 * j], uraw[4 * j + 1], uraw[4 * j + 2], uraw[4 * j + 3]};
+          store_u4<LM>(Us + buf * BK * US + (f >> 4) * US + (f & 15) * 4, f4, prm.m);
         }
       }
     } else {
@@ -628,7 +661,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
       const int e = j * NT + t;
       const int kl = u_kmajor ? (e & (BK - 1)) : (e >> 6);
       const int ql = u_kmajor ? (e >> 4) : (e & 63);
-      Us[buf * BK * US + kl * US + ql] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
+      store_u<LM>(Us + buf * BK * US + kl * US + ql, __float_as_uint(uraw[j]), prm.m);
     }
     }
     if (HAZARD_CHECK) {
@@ -884,18 +917,14 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
 #pragma unroll
       for (int j = 0; j < NU / 4; ++j) {
         const int f = j * NT + t;
-        uint4 wu;
-        wu.x = enc_u<LM>(__float_as_uint(uraw[4 * j]), prm.m);
-        wu.y = enc_u<LM>(__float_as_uint(uraw[4 * j + 1]), prm.m);
-        wu.z = enc_u<LM>(__float_as_uint(uraw[4 * j + 2]), prm.m);
-        wu.w = enc_u<LM>(__float_as_uint(uraw[4 * j + 3]), prm.m);
-        *reinterpret_cast<uint4*>(Us + buf * BK * US + (f >> 4) * US + (f & 15) * 4) = wu;
+        const float f4[4] = {uraw[4 * j], uraw[4 * j + 1], uraw[4 * j + 2], uraw[4 * j + 3]};
+        store_u4<LM>(Us + buf * BK * US + (f >> 4) * US + (f & 15) * 4, f4, prm.m);
       }
     } else {
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
-      Us[buf * BK * US + (e >> 6) * US + (e & 63)] = enc_u<LM>(__float_as_uint(uraw[j]), prm.m);
+      store_u<LM>(Us + buf * BK * US + (e >> 6) * US + (e & 63), __float_as_uint(uraw[j]), prm.m);
     }
     }
     if (HAZARD_CHECK) {
