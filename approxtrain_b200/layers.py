@@ -80,7 +80,8 @@ class _ConvamBiasActFn(torch.autograd.Function):
     def backward(ctx, dy):
         x, w, y = ctx.saved_tensors
         strides, padding, lut, det, has_bias = ctx.cfg
-        g = dy * (y > 0) if y is not None else dy
+        # ReLU gradient as one kernel: dy where the output was positive, +0 elsewhere (TF's ReluGrad)
+        g = torch.ops.aten.threshold_backward(dy, y, 0.0) if y is not None else dy
         g = g.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
@@ -104,7 +105,7 @@ class _DenseamBiasActFn(torch.autograd.Function):
     def backward(ctx, dy):
         x, w, y = ctx.saved_tensors
         lut, det, has_bias = ctx.cfg
-        g = (dy * (y > 0) if y is not None else dy).contiguous()
+        g = (torch.ops.aten.threshold_backward(dy, y, 0.0) if y is not None else dy).contiguous()
         dx, dw = ops.denseam_grad(g, x, w, lut, deterministic=det)
         db = g.sum(0) if has_bias and ctx.needs_input_grad[2] else None
         return dx, dw, db, None, None, None
