@@ -454,23 +454,25 @@ int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   return AMSIM_OK;
 }
 
-template <int TQ, int LM>
+template <int TQ, int NW, int LM>
 int launch_fgrad_thin_t(cudaStream_t st, Params& p, int device) {
-  p.tile_bytes = (2 * THIN_BK * 32 + 2 * THIN_BK * 4 * TQ) * 4;
+  p.tile_bytes = (2 * THIN_BK * 32 + 2 * THIN_BK * NW * TQ) * 4;
   const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
-  int rc = ensure_smem(fgrad_exact_thin<TQ, LM>, smem, device);
+  int rc = ensure_smem(fgrad_exact_thin<TQ, NW, LM>, smem, device);
   if (rc) return rc;
-  dim3 grid((p.P + 31) / 32, (p.Q + 4 * TQ - 1) / (4 * TQ), 1);
+  dim3 grid((p.P + 31) / 32, (p.Q + NW * TQ - 1) / (NW * TQ), 1);
   AMSIM_COUNT_LAUNCH();
-  fgrad_exact_thin<TQ, LM><<<grid, 128, smem, st>>>(p);
+  fgrad_exact_thin<TQ, NW, LM><<<grid, 32 * NW, smem, st>>>(p);
   CUDA_TRY(cudaGetLastError());
   return AMSIM_OK;
 }
 template <int LM>
 int launch_fgrad_thin(cudaStream_t st, Params& p, int tq, int device) {
-  if (tq == 4) return launch_fgrad_thin_t<4, LM>(st, p, device);
-  if (tq == 2) return launch_fgrad_thin_t<2, LM>(st, p, device);
-  return launch_fgrad_thin_t<1, LM>(st, p, device);
+  // 16 warps per CTA share one staged V tile when the output is wide enough to use them
+  const bool wide = (p.Q + tq - 1) / tq > 4 && !getenv("AMSIM_THIN_NARROW");
+  if (tq == 4) return wide ? launch_fgrad_thin_t<4, 16, LM>(st, p, device) : launch_fgrad_thin_t<4, 4, LM>(st, p, device);
+  if (tq == 2) return wide ? launch_fgrad_thin_t<2, 16, LM>(st, p, device) : launch_fgrad_thin_t<2, 4, LM>(st, p, device);
+  return wide ? launch_fgrad_thin_t<1, 16, LM>(st, p, device) : launch_fgrad_thin_t<1, 4, LM>(st, p, device);
 }
 
 int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_bytes, int device) {

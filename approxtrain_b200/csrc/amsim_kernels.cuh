@@ -1014,15 +1014,15 @@ AMSIM_UNROLL_K
 // Every output is one serial FP32 chain over the whole reduction (the reference's order),
 // so the only parallelism is the number of outputs: with 64 chains per thread (fgrad_gemm)
 // a 576 x 64 gradient occupies five CTAs.  Here a thread owns TQ chains (one p, TQ
-// consecutive q), a CTA covers 32 p x 4*TQ q.  grid = (ceil(P/32), ceil(Q/(4*TQ))).
+// consecutive q), a CTA of NW warps covers 32 p x NW*TQ q.  grid = (ceil(P/32), ceil(Q/(NW*TQ))).
 // -----------------------------------------------------------------------------
 constexpr int THIN_BK = 16;
 
-template <int TQ, int LM>
-__global__ void __launch_bounds__(128) fgrad_exact_thin(const Params prm) {
-  constexpr int NT = 128, BPT = 32, BQT = 4 * TQ;
+template <int TQ, int NW, int LM>
+__global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
+  constexpr int NT = 32 * NW, BPT = 32, BQT = NW * TQ;  // NW warps share one staged V tile
   constexpr int BK = THIN_BK;
-  constexpr int NV = BK / 4;                      // V rows staged per thread
+  constexpr int NV = BK / NW;                     // V rows staged per thread
   constexpr int NUQ = (BK * BQT + NT - 1) / NT;   // U elements staged per thread
   extern __shared__ __align__(16) uint8_t smem[];
   uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);  // [2][BK][32]
@@ -1050,7 +1050,7 @@ __global__ void __launch_bounds__(128) fgrad_exact_thin(const Params prm) {
   auto load_tile = [&](int kb) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      const int pix = kb * BK + w + 4 * i;
+      const int pix = kb * BK + w + NW * i;
       float val = 0.f;
       if (pv && pix < prm.K) {
         const uint32_t n = fdiv((uint32_t)pix, g.d_img);
@@ -1074,7 +1074,7 @@ __global__ void __launch_bounds__(128) fgrad_exact_thin(const Params prm) {
   auto store_tile = [&](int buf) {
 #pragma unroll
     for (int i = 0; i < NV; ++i)
-      Vs[(buf * BK + w + 4 * i) * BPT + lane] = enc_v<true, LM>(__float_as_uint(vraw[i]), prm.m);
+      Vs[(buf * BK + w + NW * i) * BPT + lane] = enc_v<true, LM>(__float_as_uint(vraw[i]), prm.m);
 #pragma unroll
     for (int j = 0; j < NUQ; ++j) {
       const int e = j * NT + t;
