@@ -287,6 +287,28 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   p.tile_bytes = L::TILE_BYTES;
   const size_t smem_plain = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
 
+  // Fast mode, narrow outputs (at most 32 columns: first-layer input gradients, small heads, LeNet-5's
+  // convolutions): 2 or 4 warps share each 16-column group and split the reduction steps.
+  if constexpr (!EXACT && !lm_direct(LM)) {
+    const int qs = p.Q <= 16 ? 4 : p.Q <= 32 ? 2 : 1;
+    if (qs > 1 && nkb >= 2 && !getenv("AMSIM_NO_QSPLIT")) {
+      const int qt = (p.Q + BQ / qs - 1) / (BQ / qs);
+      if (qs == 4) {
+        int rc = ensure_smem(gather_gemm<1, EXACT, VEC, GM_PLAIN, LM, 4>, smem_plain, device);
+        if (rc) return rc;
+        AMSIM_COUNT_LAUNCH();
+        gather_gemm<1, EXACT, VEC, GM_PLAIN, LM, 4><<<dim3(ptiles, qt, batch), L::NT, smem_plain, st>>>(p);
+      } else {
+        int rc = ensure_smem(gather_gemm<1, EXACT, VEC, GM_PLAIN, LM, 2>, smem_plain, device);
+        if (rc) return rc;
+        AMSIM_COUNT_LAUNCH();
+        gather_gemm<1, EXACT, VEC, GM_PLAIN, LM, 2><<<dim3(ptiles, qt, batch), L::NT, smem_plain, st>>>(p);
+      }
+      CUDA_TRY(cudaGetLastError());
+      return AMSIM_OK;
+    }
+  }
+
   // Fast mode, balanced launch: the plain grid would leave the last wave of resident CTA slots
   // partly empty (or never fill them), so the (tile, reduction block) pairs are dealt out in
   // equal runs to exactly as many CTAs as the device holds.  Not taken while the stream is

@@ -456,10 +456,15 @@ __device__ __forceinline__ long long balanced_begin(long long c, long long iters
   return c * iters / grid;
 }
 
-template <int WP, bool EXACT, bool VEC, int MODE, int LM>
+// QS (fast mode, plain grid, narrow outputs Q <= 64 / QS): the CTA's four warps would mostly idle
+// on a 64-column tile, so the tile is 64 / QS columns wide and QS warps share each 16-column
+// group, taking every QS-th reduction step; their register tiles are added in warp order at the end.
+template <int WP, bool EXACT, bool VEC, int MODE, int LM, int QS = 1>
 __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_gemm(const Params prm) {
   using L = SmemLayout<WP>;
   constexpr int NT = L::NT, BP = L::BP, VS = L::VS;
+  constexpr int BQE = BQ / QS;  // columns this CTA produces
+  static_assert(QS == 1 || (WP == 1 && !EXACT && MODE == GM_PLAIN), "warps share columns only in plain fast launches");
   constexpr int NU = BK * BQ / NT;  // U elements staged per thread
   constexpr bool CLUSTER = MODE == GM_CLUSTER;
   constexpr bool BALANCED = MODE == GM_BALANCED;
@@ -474,7 +479,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   uint8_t* lut_s = smem + (lut_base - smem_base);
 
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
-  const int wp = w % WP, wq = w / WP;
+  const int wp = w % WP, wq = (w / WP) / QS, ksub = (w / WP) % QS;  // column group, share of the reduction steps
   const int ksplit = CLUSTER ? prm.ksplit : 1;   // cluster size along x
   const int krank = blockIdx.x % ksplit;         // this CTA's slice of the reduction
   const Gather& g = prm.g;
@@ -509,7 +514,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
     kb_begin = krank * per;
     nkb = min(kb_begin + per, nkb_all);
   }
-  const int p0 = tile_p * BP, q0 = tile_q * BQ;
+  const int p0 = tile_p * BP, q0 = tile_q * BQE;
   const float* __restrict__ Vg = prm.V + (long long)tile_z * prm.v_bs;
   const float* __restrict__ Ug = prm.U + (long long)tile_z * prm.u_bs;
   float* __restrict__ Og = prm.O + (long long)tile_z * prm.o_bs;
@@ -596,7 +601,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
         const int ql = prm.u_vec == 2 ? (f >> 2) : (f & 15) * 4;
         const int kglob = kb * BK + kl, qg = q0 + ql;
         float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (kglob < prm.K && qg < prm.Q) {
+        if (kglob < prm.K && qg < prm.Q && ql < BQE) {
           const uint32_t tap = fdiv((uint32_t)kglob, g.d_sc);
           const int kk = kglob - (int)tap * g.SC;
           const int tj = (int)fdiv(tap, g.d_kw);
@@ -615,7 +620,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
       const int ql = u_kmajor ? (e >> 4) : (e & 63);
       const int kglob = kb * BK + kl, qg = q0 + ql;
       float val = 0.f;
-      if (kglob < prm.K && qg < prm.Q) {
+      if (kglob < prm.K && qg < prm.Q && ql < BQE) {
         const uint32_t tap = fdiv((uint32_t)kglob, g.d_sc);
         const int kk = kglob - (int)tap * g.SC;
         const int tj = (int)fdiv(tap, g.d_kw);
@@ -712,6 +717,13 @@ AMSIM_UNROLL_K
           mac_step<true, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
                              prm.lut_raw);
       }
+    } else if (QS > 1) {
+AMSIM_UNROLL_K
+      for (int kq = 0; kq < BK / QS; ++kq) {
+        const int kk = kq * QS + ksub;
+        mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
+                            prm.lut_raw);
+      }
     } else {
 AMSIM_UNROLL_K
       for (int kk = 0; kk < BK; ++kk)
@@ -720,6 +732,27 @@ AMSIM_UNROLL_K
     }
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
+  }
+
+  // ---- warps that shared a column group: add their register tiles in warp order ----------
+  if (QS > 1) {
+    float* red = reinterpret_cast<float*>(smem);  // [QS - 1][TR*TC][32 * (4 / QS)], the operand tiles are dead now
+    constexpr int GT = 32 * (4 / QS);             // threads per share
+    const int gt = wq * 32 + lane;                // this thread's slot within its share
+    if (ksub != 0) {
+#pragma unroll
+      for (int r = 0; r < TR; ++r)
+#pragma unroll
+        for (int c = 0; c < TC; ++c) red[((ksub - 1) * TR * TC + r * TC + c) * GT + gt] = acc[r][c];
+    }
+    __syncthreads();
+    if (ksub != 0) return;
+    for (int src = 1; src < QS; ++src) {
+#pragma unroll
+      for (int r = 0; r < TR; ++r)
+#pragma unroll
+        for (int c = 0; c < TC; ++c) acc[r][c] = __fadd_rn(acc[r][c], red[((src - 1) * TR * TC + r * TC + c) * GT + gt]);
+    }
   }
 
   // ---- cluster reduction: ranks 1.. park their register tiles in their own shared

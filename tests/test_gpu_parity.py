@@ -164,15 +164,17 @@ def test_conv_every_lut(ops, oracle, luts, name):
             oracle.conv2d_bwd_input(g, wt, dy, lut, m), f"igrad {name}")
 
 
-def test_fast_forward_is_bit_exact_without_zero_operands(ops, oracle, luts):
+def test_fast_forward_is_bit_exact_without_zero_operands(ops, oracle, luts, monkeypatch):
     """With no zero/denormal operand and no underflowing product the fast path
-    computes the reference products exactly and sums them in the reference
-    order: VALID padding, N(0,1) data."""
+    computes the reference products exactly and, where one warp of one CTA owns an
+    output's whole reduction (more than 32 output columns, plain grid), sums them in
+    the reference order: VALID padding, N(0,1) data."""
+    monkeypatch.setenv("AMSIM_BALANCED", "0")
     lut, m = luts["MBM_7"]
     rng = np.random.default_rng(17)
     x = rng.standard_normal((2, 12, 12, 8)).astype(np.float32)
-    wt = rng.standard_normal((3, 3, 8, 32)).astype(np.float32)
-    g = oracle.geometry(2, 12, 12, 8, 3, 3, 32, 1, 1, "VALID")
+    wt = rng.standard_normal((3, 3, 8, 48)).astype(np.float32)
+    g = oracle.geometry(2, 12, 12, 8, 3, 3, 48, 1, 1, "VALID")
     y = ops.convam(dev(x), dev(wt), [1, 1, 1, 1], "VALID", mant_mul_lut=lut_path("MBM_7")).cpu().numpy()
     assert_bit_equal(y, oracle.conv2d_fwd(g, x, wt, lut, m), "fast fwd, no zeros")
 
@@ -947,3 +949,36 @@ def test_tables_with_16_bit_entries(ops, oracle, m, tmp_path):
     np.zeros(3 << 10, np.uint8).tofile(bad)     # neither 2^(2m) nor twice that
     with pytest.raises(Exception):
         ops.am_multiply(dev(a), dev(a), bad)
+
+
+@pytest.mark.parametrize("off", [None, "1"])
+def test_narrow_outputs_share_column_groups_between_warps(ops, oracle, luts, off, monkeypatch):
+    """Outputs of at most 32 columns (a 3-channel image gradient, LeNet-5's 6 and 16 filters, a
+    10-class head): 2 or 4 warps take the same columns and every 2nd / 4th reduction step, and
+    their register tiles are added in warp order.  Fast mode only; same bar, run-to-run identical,
+    fused epilogue and strided (stride-phase) outputs included."""
+    if off:
+        monkeypatch.setenv("AMSIM_NO_QSPLIT", off)
+    rng = np.random.default_rng(321)
+    for name in ("MBM_7", "MIT_7"):
+        lut, m = luts[name]
+        path = lut_path(name)
+        for (n, h, w, c, kh, kw, k, s, pad) in [(2, 20, 20, 3, 7, 7, 16, 2, "VALID"),   # input gradient has 3 columns
+                                                (4, 28, 28, 1, 5, 5, 6, 1, "SAME"),     # LeNet-5 conv1
+                                                (4, 14, 14, 6, 5, 5, 16, 1, "VALID"),   # LeNet-5 conv2
+                                                (2, 9, 9, 32, 3, 3, 20, 1, "SAME")]:    # 20 columns: two warps per group
+            x, wt = _conv_case(rng, n, h, w, c, kh, kw, k)
+            g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+            dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+            b = rng.standard_normal(k).astype(np.float32)
+            kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=path)
+            y = ops.convam(dev(x), dev(wt), **kw_)
+            assert_close(y.cpu().numpy(), oracle.conv2d_fwd(g, x, wt, lut, m), f"narrow fwd {name}")
+            assert torch.equal(y, ops.convam(dev(x), dev(wt), **kw_))
+            dx = ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_).cpu().numpy()
+            assert_close(dx, oracle.conv2d_bwd_input(g, wt, dy, lut, m), f"narrow input-grad {name}")
+            fused = ops.convam_bias_act(dev(x), dev(wt), dev(b), activation="relu", **kw_)
+            assert torch.equal(fused, torch.relu(y + dev(b)))
+        xd = rng.standard_normal((256, 84)).astype(np.float32)
+        wd = rng.standard_normal((84, 10)).astype(np.float32)
+        assert_close(ops.denseam(dev(xd), dev(wd), path).cpu().numpy(), oracle.dense_fwd(xd, wd, lut, m), f"narrow dense {name}")
