@@ -325,7 +325,9 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
     const long long waves = (ctas + slots - 1) / slots;
     const double fill = (double)ctas / (double)(waves * slots);
     long long grid = slots;
-    if (iters / grid < 8) grid = iters / 8;  // at least 8 reduction blocks per CTA
+    // small problems are latency bound (a lone warp needs ~5 us per reduction block): spread them
+    // down to 2 reduction blocks per CTA
+    if (iters / grid < 2) grid = iters / 2;
     // measured: pays when the plain grid is at most two waves with a last wave under ~93 % full
     // (one wave at 88 %: -7 %); with more waves the plain grid's tail is already short
     int mode = waves <= 2 && fill < 0.93 && grid >= 2 && nkb >= 2;
@@ -366,7 +368,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   int ksplit = 1;
   if (!EXACT && !lm_global(LM)) {
     const int slots = 148 * AMSIM_CTAS1;
-    while (ksplit < 8 && ctas * (ksplit * 2) <= slots && nkb / (ksplit * 2) >= 6) ksplit *= 2;
+    while (ksplit < 8 && ctas * (ksplit * 2) <= slots && nkb / (ksplit * 2) >= 2) ksplit *= 2;
     if (const char* f = getenv("AMSIM_FORCE_KSPLIT")) ksplit = atoi(f) > 0 ? atoi(f) : 1;
   }
   p.ksplit = ksplit;
@@ -431,21 +433,46 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
 
 struct FgradPlan {
   int wp, splits, k_chunk;
+  int thin, tq;  // one-to-four-chains-per-thread kernel instead of the 128 x 64 tiles
   size_t ws_bytes;
 };
 
+// How a filter / weight gradient of P x Q outputs over a reduction of K runs.  Depends on the
+// dimensions, the mode and the environment only, so the *_workspace functions and the launch agree.
 FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
   FgradPlan f;
   f.wp = 1;  // 128-row tiles: 3 CTAs of 4 warps per SM without register spills
   const int bp = f.wp * 128;
   const int slots = 148 * (f.wp == 1 ? 3 : 2);  // resident CTAs on the whole GPU
   const long long tiles = (long long)((P + bp - 1) / bp) * ((Q + BQ - 1) / BQ);
+  const long long chains = (long long)P * Q;
+  f.thin = 0;
+  f.tq = 1;
   int splits = 1;
-  if (!exact && tiles > 0) {
-    // one balanced wave: as many splits as fit in the resident slots
-    splits = (int)(slots / tiles);
-    const int max_splits = (K + 4 * BK - 1) / (4 * BK);  // at least 4 stages per split
-    if (splits > max_splits) splits = max_splits;
+  if (exact) {
+    // Deterministic mode cannot split a reduction; when the 128 x 64 tiles would fill less than
+    // half of the resident CTA slots, threads take fewer chains each so the whole device works.
+    f.thin = tiles * 2 < slots;
+    if (const char* e = getenv("AMSIM_THIN_FGRAD")) f.thin = atoi(e) != 0;
+    f.tq = chains >= 4ll * 32 * 4 * 148 * 2 ? 4 : chains >= 2ll * 32 * 4 * 148 * 2 ? 2 : 1;
+    if (const char* e = getenv("AMSIM_THIN_TQ")) f.tq = atoi(e);
+  } else if (tiles > 0) {
+    // Fast mode, tiny outputs (LeNet-5's 5x5x1x6 filter: 150 of a tile's 8192 outputs): one chain per
+    // thread over a slice of the reduction wastes nothing on padding; many slices, summed in order.
+    f.thin = (double)chains < 0.2 * (double)(tiles * bp * BQ);
+    if (const char* e = getenv("AMSIM_THIN_FAST")) f.thin = atoi(e) != 0;
+    if (f.thin) {
+      const int nw = (Q + f.tq - 1) / f.tq > 4 ? 16 : 4;
+      const long long ctas = (long long)((P + 31) / 32) * ((Q + nw * f.tq - 1) / (nw * f.tq));
+      splits = (int)(4 * 148 / ctas);
+      const int max_splits = (K + 2 * BK - 1) / (2 * BK);  // at least 2 stages per split
+      if (splits > max_splits) splits = max_splits;
+    } else {
+      // one balanced wave: as many splits as fit in the resident slots
+      splits = (int)(slots / tiles);
+      const int max_splits = (K + 4 * BK - 1) / (4 * BK);  // at least 4 stages per split
+      if (splits > max_splits) splits = max_splits;
+    }
     if (splits < 1) splits = 1;
   }
   int chunk = (K + splits - 1) / splits;
@@ -456,7 +483,6 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
   f.ws_bytes = f.splits > 1 ? (size_t)f.splits * P * Q * sizeof(float) : 0;
   return f;
 }
-
 template <bool EXACT, bool VEC, int LM>
 int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   using L = SmemLayout<1>;
@@ -482,10 +508,16 @@ int launch_fgrad_thin_t(cudaStream_t st, Params& p, int device) {
   const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
   int rc = ensure_smem(fgrad_exact_thin<TQ, NW, LM>, smem, device);
   if (rc) return rc;
-  dim3 grid((p.P + 31) / 32, (p.Q + NW * TQ - 1) / (NW * TQ), 1);
+  dim3 grid((p.P + 31) / 32, (p.Q + NW * TQ - 1) / (NW * TQ), p.splits);
   AMSIM_COUNT_LAUNCH();
   fgrad_exact_thin<TQ, NW, LM><<<grid, 32 * NW, smem, st>>>(p);
   CUDA_TRY(cudaGetLastError());
+  if (p.splits > 1) {
+    const long long n = (long long)p.P * p.Q;
+    AMSIM_COUNT_LAUNCH();
+    reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq);
+    CUDA_TRY(cudaGetLastError());
+  }
   return AMSIM_OK;
 }
 template <int LM>
@@ -509,16 +541,10 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   p.splits = f.splits;
   p.k_chunk = f.k_chunk;
   p.ws = static_cast<float*>(ws);
-  if (exact) {
-    // Deterministic mode cannot split a reduction; when the 128 x 64 tiles would fill less than
-    // half of the resident CTA slots, threads take fewer chains each so the whole device works.
-    const long long fat = (long long)((p.P + 127) / 128) * ((p.Q + BQ - 1) / BQ);
-    const long long chains = (long long)p.P * p.Q;
-    int thin = fat * 2 < 148 * AMSIM_CTAS1;
-    if (const char* e = getenv("AMSIM_THIN_FGRAD")) thin = atoi(e) != 0;
-    if (thin) {
-      int tq = chains >= 4ll * 32 * 4 * 148 * 2 ? 4 : chains >= 2ll * 32 * 4 * 148 * 2 ? 2 : 1;
-      if (const char* e = getenv("AMSIM_THIN_TQ")) tq = atoi(e);
+  if (f.thin) {
+    {
+      const int tq = f.tq;
+      p.flush_zero = exact ? 0 : 1;
       if (p.lut_mode == LM_DIRECT_MBM) return launch_fgrad_thin<LM_DIRECT_MBM>(st, p, tq, device);
       if (p.lut_mode == LM_DIRECT_MIT) return launch_fgrad_thin<LM_DIRECT_MIT>(st, p, tq, device);
       if (p.lut_mode == LM_ADD) return launch_fgrad_thin<LM_ADD>(st, p, tq, device);

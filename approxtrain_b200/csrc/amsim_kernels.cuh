@@ -149,6 +149,7 @@ struct Params {
   int v_trans;
   long long v_ld;
   int u_vec;                    // gather_gemm: 128-bit loads of U along q (1) or along k (2); 0 = scalar
+  int flush_zero;               // fgrad_exact_thin in fast mode: an operand with exponent field 0 gives a zero product
   int exact_only;               // deterministic kernels: never take the fast arithmetic, even for hazard-free stages
   // fgrad only
   int k_chunk, splits;
@@ -1068,6 +1069,9 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
   const int w = __shfl_sync(0xffffffffu, t >> 5, 0);
   const int p0 = blockIdx.x * BPT, q0 = blockIdx.y * BQT;
   const Gather& g = prm.g;
+  // this CTA's slice of the reduction (the whole of it unless fast mode asked for splits)
+  const int kbeg = blockIdx.z * prm.k_chunk;
+  const int kend = min(kbeg + prm.k_chunk, prm.K);
   const float* __restrict__ Vg = prm.V;
   const float* __restrict__ Ug = prm.U;
   if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
@@ -1083,9 +1087,9 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
   auto load_tile = [&](int kb) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      const int pix = kb * BK + w + NW * i;
+      const int pix = kbeg + kb * BK + w + NW * i;
       float val = 0.f;
-      if (pv && pix < prm.K) {
+      if (pv && pix < kend) {
         const uint32_t n = fdiv((uint32_t)pix, g.d_img);
         const uint32_t rem = (uint32_t)pix - n * (uint32_t)(g.PH * g.PW);
         const uint32_t a = fdiv(rem, g.d_pw);
@@ -1099,8 +1103,8 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
 #pragma unroll
     for (int j = 0; j < NUQ; ++j) {
       const int e = j * NT + t;
-      const int pix = kb * BK + e / BQT, qg = q0 + e % BQT;
-      uraw[j] = (e < BK * BQT && pix < prm.K && qg < prm.Q)
+      const int pix = kbeg + kb * BK + e / BQT, qg = q0 + e % BQT;
+      uraw[j] = (e < BK * BQT && pix < kend && qg < prm.Q)
                     ? __ldg(Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq) : 0.f;
     }
   };
@@ -1118,7 +1122,7 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
   float acc[TQ];
 #pragma unroll
   for (int r = 0; r < TQ; ++r) acc[r] = 0.f;
-  const int nkb = (prm.K + BK - 1) / BK;
+  const int nkb = (kend - kbeg + BK - 1) / BK;
   if (nkb > 0) {
     load_tile(0);
     store_tile(0);
@@ -1135,7 +1139,9 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
       // same arithmetic as the deterministic branch of mac_step
       const uint32_t ci = lm_global(LM) ? (wv & prm.cmask) : ((wv & 0xFFu) | lut_base);
       const uint32_t cs = (LM == LM_ADD ? wv : (wv & 0xFF800000u)) - 0x3F800000u;
-      const int cn = (int)(0x3F800000u - (wv & 0x7F800000u));
+      // fast mode treats zero / denormal operands as exact zeros (as the tiled fast kernels do): an
+      // unreachable threshold switches the lane operand's products off
+      const int cn = (prm.flush_zero && !(wv & 0x7F800000u)) ? 0x7FFFFFFF : (int)(0x3F800000u - (wv & 0x7F800000u));
 #pragma unroll
       for (int r = 0; r < TQ; ++r) {
         const uint32_t uu = us[kk * BQT + r];
@@ -1153,7 +1159,7 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
         } else {
           e = lds_u8((uu & prm.rmask) | ci) * prm.mult;
         }
-        if (ee > cn) acc[r] = __fadd_rn(acc[r], __uint_as_float(e + (pp + cs)));
+        if (ee > cn && !(prm.flush_zero && ee == 0)) acc[r] = __fadd_rn(acc[r], __uint_as_float(e + (pp + cs)));
       }
     }
     if (kb + 1 < nkb) store_tile(buf ^ 1);
@@ -1163,7 +1169,10 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
 #pragma unroll
     for (int r = 0; r < TQ; ++r) {
       const int qg = q0 + w * TQ + r;
-      if (qg < prm.Q) prm.O[(long long)pg * prm.o_sp + (long long)qg * prm.o_sq] = acc[r];
+      if (qg < prm.Q) {
+        if (prm.splits > 1) prm.ws[((long long)blockIdx.z * prm.P + pg) * prm.Q + qg] = acc[r];
+        else prm.O[(long long)pg * prm.o_sp + (long long)qg * prm.o_sq] = acc[r];
+      }
     }
   }
 }

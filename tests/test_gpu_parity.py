@@ -170,6 +170,7 @@ def test_fast_forward_is_bit_exact_without_zero_operands(ops, oracle, luts, monk
     output's whole reduction (more than 32 output columns, plain grid), sums them in
     the reference order: VALID padding, N(0,1) data."""
     monkeypatch.setenv("AMSIM_BALANCED", "0")
+    monkeypatch.setenv("AMSIM_FORCE_KSPLIT", "1")
     lut, m = luts["MBM_7"]
     rng = np.random.default_rng(17)
     x = rng.standard_normal((2, 12, 12, 8)).astype(np.float32)
