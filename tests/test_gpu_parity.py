@@ -312,7 +312,11 @@ def test_matmul_transposes_in_the_kernel_and_alpha(ops, oracle, luts, ta, tb):
     lut, m = luts["MBM_7"]
     p7 = lut_path("MBM_7")
     rng = np.random.default_rng(12)
-    M, K, N = 37, 70, 45
+    for (M, K, N) in ((37, 70, 45), (40, 72, 48)):   # scalar staging; 128-bit staging along q or k
+        _check_matmul_transposes(ops, oracle, lut, m, p7, rng, M, K, N, ta, tb)
+
+
+def _check_matmul_transposes(ops, oracle, lut, m, p7, rng, M, K, N, ta, tb):
     def mk(batch, r, c, t):
         shp = (c, r) if t else (r, c)
         return rng.standard_normal(batch + shp).astype(np.float32)
@@ -328,7 +332,7 @@ def test_matmul_transposes_in_the_kernel_and_alpha(ops, oracle, luts, ta, tb):
         assert_close(fast.cpu().numpy().reshape(want.shape), want, f"fast ta={ta} tb={tb} {ba} {bb}")
         for det in (True, False):
             base = ops.matmulam(dev(a), dev(b), transpose_a=ta, transpose_b=tb, mant_mul_lut=p7, deterministic=det)
-            al = float(np.float32(1.0) / np.float32(np.sqrt(70.0)))
+            al = float(np.float32(1.0) / np.float32(np.sqrt(float(K))))
             sc = ops.matmulam(dev(a), dev(b), transpose_a=ta, transpose_b=tb, mant_mul_lut=p7, deterministic=det, alpha=al)
             assert torch.equal(sc, base * al), "alpha is one FP32 multiply"
 
