@@ -26,9 +26,18 @@
 // FFMA rounds exactly like the reference's "accumulator + product" add).
 // What bounds it: each lookup returns 4 bytes per lane through the 128-byte/clk
 // shared-memory return path, i.e. 32 products per clock per SM at most; the
-// operand words fetched from shared memory share that path, which is why the
-// uniform operand is packed into ONE word per element.  Tensor cores cannot be
-// used: no product is a hardware multiply.
+// operand words fetched from shared memory share that path (the lane operand
+// is ONE packed word per element; the uniform operand is kept as two words,
+// sign+exponent and table row, because unpacking it in the loop costs more
+// issue slots than the second broadcast load costs wavefronts).  Tensor cores
+// cannot be used: no product is a hardware multiply.
+//
+// Besides the plain grid (one CTA per 128 x 64 tile) gather_gemm has a balanced
+// mode (equal runs of (tile, reduction block) pairs over exactly the resident
+// CTAs, shared tiles combined in CTA order by the CTA that finishes last), a
+// cluster mode (the same split through distributed shared memory, used under
+// graph capture) and a narrow-output mode (several warps share a column group);
+// fgrad_exact_thin serves outputs too small for the 128 x 64 tiles.
 #pragma once
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
