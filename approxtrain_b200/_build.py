@@ -27,13 +27,32 @@ def needs_build() -> bool:
     return any(os.path.exists(f) and os.path.getmtime(f) > t for f in SOURCES + HEADERS)
 
 
+DRIVER_SRC = os.path.join(_PKG, "csrc", "abi_driver.c")
+DRIVER_PATH = os.path.join(_PKG, "abi_driver")
+
+
+def build_driver() -> str:
+    """The plain-C program over the C ABI (csrc/abi_driver.c): gcc, the header, libamsim.so
+    and the CUDA runtime for its device buffers.  Proves the header is C and the library
+    usable without Python or C++."""
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    subprocess.check_call([
+        os.environ.get("CC", "gcc"), "-std=c99", "-O1", "-Wall", "-o", DRIVER_PATH, DRIVER_SRC,
+        "-I", os.path.join(os.path.dirname(_PKG), "include"), "-I", os.path.join(cuda, "include"),
+        "-L", _PKG, "-lamsim", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-lm",
+        "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")])
+    return DRIVER_PATH
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Build libamsim.so if it is missing or older than its sources."""
-    if not force and not needs_build():
-        return LIB_PATH
-    nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + SOURCES
-    subprocess.check_call(cmd)
+    """Build libamsim.so (and the C driver) if missing or older than the sources."""
+    if force or needs_build():
+        nvcc = os.environ.get("NVCC", "nvcc")
+        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + SOURCES
+        subprocess.check_call(cmd)
+    if force or not os.path.exists(DRIVER_PATH) or os.path.getmtime(DRIVER_PATH) < max(
+            os.path.getmtime(DRIVER_SRC), os.path.getmtime(LIB_PATH)):
+        build_driver()
     return LIB_PATH
 
 

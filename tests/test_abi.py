@@ -98,3 +98,11 @@ def test_ops_reject_cpu_tensors_and_bad_arguments(L):
     assert ops._hw([1, 2, 3, 1], "strides") == (2, 3)
     with pytest.raises(ValueError):
         ops._hw([2, 1, 1, 1], "strides")
+
+
+def test_header_is_valid_c99_and_cxx11():
+    """include/amsim.h is the whole boundary: it has to compile as C and as C++ on its own."""
+    import subprocess
+    hdr = os.path.join(ROOT, "include", "amsim.h")
+    subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-x", "c", hdr])
+    subprocess.check_call(["g++", "-std=c++11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", hdr])

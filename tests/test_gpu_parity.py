@@ -987,3 +987,18 @@ def test_narrow_outputs_share_column_groups_between_warps(ops, oracle, luts, off
         xd = rng.standard_normal((256, 84)).astype(np.float32)
         wd = rng.standard_normal((84, 10)).astype(np.float32)
         assert_close(ops.denseam(dev(xd), dev(wd), path).cpu().numpy(), oracle.dense_fwd(xd, wd, lut, m), f"narrow dense {name}")
+
+
+def test_plain_c_program_over_the_abi():
+    """approxtrain_b200/csrc/abi_driver.c — C99, no Python, no torch — opens a LUT, checks a
+    deterministic convolution output against the ascending chain of primitive products, runs
+    both gradients in both modes and the error path; exit code 0 means all of it passed."""
+    import subprocess
+    from approxtrain_b200 import _build
+    exe = _build.DRIVER_PATH
+    if not os.path.exists(exe):
+        _build.build_driver()
+    for name in ("MBM_7", "MIT_5"):
+        out = subprocess.run([exe, lut_path(name)], capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, out.stderr[-2000:]
+        assert "abi_driver ok" in out.stdout
