@@ -502,15 +502,15 @@ int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   return AMSIM_OK;
 }
 
-template <int TQ, int NW, int LM>
+template <int TQ, int NW, int LM, bool FLUSH>
 int launch_fgrad_thin_t(cudaStream_t st, Params& p, int device) {
   p.tile_bytes = (2 * THIN_BK * 32 + 2 * THIN_BK * NW * TQ) * 4;
   const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
-  int rc = ensure_smem(fgrad_exact_thin<TQ, NW, LM>, smem, device);
+  int rc = ensure_smem(fgrad_exact_thin<TQ, NW, LM, FLUSH>, smem, device);
   if (rc) return rc;
   dim3 grid((p.P + 31) / 32, (p.Q + NW * TQ - 1) / (NW * TQ), p.splits);
   AMSIM_COUNT_LAUNCH();
-  fgrad_exact_thin<TQ, NW, LM><<<grid, 32 * NW, smem, st>>>(p);
+  fgrad_exact_thin<TQ, NW, LM, FLUSH><<<grid, 32 * NW, smem, st>>>(p);
   CUDA_TRY(cudaGetLastError());
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
@@ -521,12 +521,29 @@ int launch_fgrad_thin_t(cudaStream_t st, Params& p, int device) {
   return AMSIM_OK;
 }
 template <int LM>
-int launch_fgrad_thin(cudaStream_t st, Params& p, int tq, int device) {
+int launch_fgrad_chain(cudaStream_t st, Params& p, int device) {
+  p.tile_bytes = (2 * BK * 32 + 2 * BK * CHAIN_Q) * 4 + 2 * BK * CHAIN_Q * 32 * 4;
+  const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
+  int rc = ensure_smem(fgrad_exact_chain<LM>, smem, device);
+  if (rc) return rc;
+  dim3 grid((p.P + 31) / 32, (p.Q + CHAIN_Q - 1) / CHAIN_Q, 1);
+  AMSIM_COUNT_LAUNCH();
+  fgrad_exact_chain<LM><<<grid, 768, smem, st>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  return AMSIM_OK;
+}
+
+template <int LM>
+int launch_fgrad_thin(cudaStream_t st, Params& p, int tq, bool flush, int device) {
   // 16 warps per CTA share one staged V tile when the output is wide enough to use them
   const bool wide = (p.Q + tq - 1) / tq > 4 && !getenv("AMSIM_THIN_NARROW");
-  if (tq == 4) return wide ? launch_fgrad_thin_t<4, 16, LM>(st, p, device) : launch_fgrad_thin_t<4, 4, LM>(st, p, device);
-  if (tq == 2) return wide ? launch_fgrad_thin_t<2, 16, LM>(st, p, device) : launch_fgrad_thin_t<2, 4, LM>(st, p, device);
-  return wide ? launch_fgrad_thin_t<1, 16, LM>(st, p, device) : launch_fgrad_thin_t<1, 4, LM>(st, p, device);
+  if (flush) {  // fast mode: tiny outputs only, one chain per thread
+    if constexpr (lm_direct(LM)) return fail(AMSIM_ERR_UNSUPPORTED, "direct models run in ordered mode");
+    else return wide ? launch_fgrad_thin_t<1, 16, LM, true>(st, p, device) : launch_fgrad_thin_t<1, 4, LM, true>(st, p, device);
+  }
+  if (tq == 4) return wide ? launch_fgrad_thin_t<4, 16, LM, false>(st, p, device) : launch_fgrad_thin_t<4, 4, LM, false>(st, p, device);
+  if (tq == 2) return wide ? launch_fgrad_thin_t<2, 16, LM, false>(st, p, device) : launch_fgrad_thin_t<2, 4, LM, false>(st, p, device);
+  return wide ? launch_fgrad_thin_t<1, 16, LM, false>(st, p, device) : launch_fgrad_thin_t<1, 4, LM, false>(st, p, device);
 }
 
 int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_bytes, int device) {
@@ -544,13 +561,24 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   if (f.thin) {
     {
       const int tq = f.tq;
-      p.flush_zero = exact ? 0 : 1;
-      if (p.lut_mode == LM_DIRECT_MBM) return launch_fgrad_thin<LM_DIRECT_MBM>(st, p, tq, device);
-      if (p.lut_mode == LM_DIRECT_MIT) return launch_fgrad_thin<LM_DIRECT_MIT>(st, p, tq, device);
-      if (p.lut_mode == LM_ADD) return launch_fgrad_thin<LM_ADD>(st, p, tq, device);
-      if (p.lut_mode == LM_GLOBAL) return launch_fgrad_thin<LM_GLOBAL>(st, p, tq, device);
-      if (p.lut_mode == LM_GLOBAL16) return launch_fgrad_thin<LM_GLOBAL16>(st, p, tq, device);
-      return launch_fgrad_thin<LM_SMEM>(st, p, tq, device);
+      const bool flush = !exact;
+      // deterministic, few chains and a long reduction: products in parallel, additions in order
+      int chain = exact && (long long)p.P * p.Q <= 2ll * 148 * 256 && p.K >= 64 * BK;
+      if (const char* e = getenv("AMSIM_CHAIN_FGRAD")) chain = exact && atoi(e) != 0;
+      if (chain) {
+        if (p.lut_mode == LM_DIRECT_MBM) return launch_fgrad_chain<LM_DIRECT_MBM>(st, p, device);
+        if (p.lut_mode == LM_DIRECT_MIT) return launch_fgrad_chain<LM_DIRECT_MIT>(st, p, device);
+        if (p.lut_mode == LM_ADD) return launch_fgrad_chain<LM_ADD>(st, p, device);
+        if (p.lut_mode == LM_GLOBAL) return launch_fgrad_chain<LM_GLOBAL>(st, p, device);
+        if (p.lut_mode == LM_GLOBAL16) return launch_fgrad_chain<LM_GLOBAL16>(st, p, device);
+        return launch_fgrad_chain<LM_SMEM>(st, p, device);
+      }
+      if (p.lut_mode == LM_DIRECT_MBM) return launch_fgrad_thin<LM_DIRECT_MBM>(st, p, tq, flush, device);
+      if (p.lut_mode == LM_DIRECT_MIT) return launch_fgrad_thin<LM_DIRECT_MIT>(st, p, tq, flush, device);
+      if (p.lut_mode == LM_ADD) return launch_fgrad_thin<LM_ADD>(st, p, tq, flush, device);
+      if (p.lut_mode == LM_GLOBAL) return launch_fgrad_thin<LM_GLOBAL>(st, p, tq, flush, device);
+      if (p.lut_mode == LM_GLOBAL16) return launch_fgrad_thin<LM_GLOBAL16>(st, p, tq, flush, device);
+      return launch_fgrad_thin<LM_SMEM>(st, p, tq, flush, device);
     }
   }
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);

@@ -158,7 +158,6 @@ struct Params {
   int v_trans;
   long long v_ld;
   int u_vec;                    // gather_gemm: 128-bit loads of U along q (1) or along k (2); 0 = scalar
-  int flush_zero;               // fgrad_exact_thin in fast mode: an operand with exponent field 0 gives a zero product
   int exact_only;               // deterministic kernels: never take the fast arithmetic, even for hazard-free stages
   // fgrad only
   int k_chunk, splits;
@@ -1061,7 +1060,8 @@ AMSIM_UNROLL_K
 // -----------------------------------------------------------------------------
 constexpr int THIN_BK = 16;
 
-template <int TQ, int NW, int LM>
+// FLUSH: fast mode (an operand with exponent field 0 gives a zero product, as in the tiled fast kernels).
+template <int TQ, int NW, int LM, bool FLUSH>
 __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
   constexpr int NT = 32 * NW, BPT = 32, BQT = NW * TQ;  // NW warps share one staged V tile
   constexpr int BK = THIN_BK;
@@ -1150,7 +1150,7 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
       const uint32_t cs = (LM == LM_ADD ? wv : (wv & 0xFF800000u)) - 0x3F800000u;
       // fast mode treats zero / denormal operands as exact zeros (as the tiled fast kernels do): an
       // unreachable threshold switches the lane operand's products off
-      const int cn = (prm.flush_zero && !(wv & 0x7F800000u)) ? 0x7FFFFFFF : (int)(0x3F800000u - (wv & 0x7F800000u));
+      const int cn = (FLUSH && !(wv & 0x7F800000u)) ? 0x7FFFFFFF : (int)(0x3F800000u - (wv & 0x7F800000u));
 #pragma unroll
       for (int r = 0; r < TQ; ++r) {
         const uint32_t uu = us[kk * BQT + r];
@@ -1168,7 +1168,7 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
         } else {
           e = lds_u8((uu & prm.rmask) | ci) * prm.mult;
         }
-        if (ee > cn && !(prm.flush_zero && ee == 0)) acc[r] = __fadd_rn(acc[r], __uint_as_float(e + (pp + cs)));
+        if (ee > cn && !(FLUSH && ee == 0)) acc[r] = __fadd_rn(acc[r], __uint_as_float(e + (pp + cs)));
       }
     }
     if (kb + 1 < nkb) store_tile(buf ^ 1);
@@ -1184,6 +1184,143 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
       }
     }
   }
+}
+
+// -----------------------------------------------------------------------------
+// fgrad_exact_chain: deterministic filter / weight gradient for outputs with few chains and a
+// long reduction (576 x 64 outputs over 200 704 pixels: 1152 warps' worth of chains).  The
+// chains have to be added in order, but their products do not have to be computed in order:
+// per 16-step stage 16 producer warps compute the stage's 16 x 8 x 32 products in parallel (warp w:
+// reduction step w for all 8 columns, lane = row; the table row is warp-uniform as everywhere)
+// into shared memory, and 8 consumer warps (warp = column, lane = row) add their own chain's 16
+// products in ascending order while the producers work on the next stage.  A product the reference returns as 0
+// is stored as +0.0, whose addition changes nothing (the accumulator is never -0.0).
+// CTA tile: 32 rows x 8 columns, 768 threads.  grid = (ceil(P/32), ceil(Q/8)).
+// -----------------------------------------------------------------------------
+constexpr int CHAIN_Q = 8;
+
+template <int LM>
+__global__ void __launch_bounds__(768) fgrad_exact_chain(const Params prm) {
+  // warps 0..15 produce (stage operands, compute one reduction step's products each), warps 16..23
+  // consume (add their chains' products), so the additions of one stage overlap the products of the next
+  constexpr int NT = 768, BPT = 32, BQT = CHAIN_Q, NPROD = 16;
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint32_t* Vs = reinterpret_cast<uint32_t*>(smem);  // [2][BK][32]
+  uint32_t* Us = Vs + 2 * BK * BPT;                  // [2][BK][8]
+  float* Ps = reinterpret_cast<float*>(Us + 2 * BK * BQT);  // [2][BK][8][32] products of two stages
+  const uint32_t smem_base = smem_addr(smem);
+  const uint32_t lut_base = (smem_base + prm.tile_bytes + prm.lut_align - 1) & ~(prm.lut_align - 1);
+  uint8_t* lut_s = smem + (lut_base - smem_base);
+
+  const int t = threadIdx.x, lane = t & 31;
+  const int w = __shfl_sync(0xffffffffu, t >> 5, 0);
+  const int p0 = blockIdx.x * BPT, q0 = blockIdx.y * BQT;
+  const Gather& g = prm.g;
+  const float* __restrict__ Vg = prm.V;
+  const float* __restrict__ Ug = prm.U;
+  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+
+  const uint32_t pg = (uint32_t)(p0 + lane);
+  const bool pv = pg < (uint32_t)prm.P;
+  const uint32_t tap = fdiv(pg, g.d_sc);
+  const int ch = (int)(pg - tap * (uint32_t)g.SC);
+  const int kh = (int)fdiv(tap, g.d_kw);
+  const int kw = (int)tap - kh * g.KW;
+
+  // Little arithmetic per staged element, so the global loads run PF stages ahead of their use:
+  // register slots vq[slot], uq[slot], filled PF iterations before they are stored to shared memory.
+  constexpr int PF = 4;
+  float vq[PF][1], uq[PF];
+  auto load_tile = [&](int kb, float (&vraw)[1], float& uraw) {
+    {
+      const int pix = kb * BK + w;
+      float val = 0.f;
+      if (pv && pix < prm.K) {
+        const uint32_t n = fdiv((uint32_t)pix, g.d_img);
+        const uint32_t rem = (uint32_t)pix - n * (uint32_t)(g.PH * g.PW);
+        const uint32_t a = fdiv(rem, g.d_pw);
+        const uint32_t b = rem - a * (uint32_t)g.PW;
+        const int u = (int)a * g.ps_h - g.off_t + kh, v = (int)b * g.ps_w - g.off_l + kw;
+        if ((unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
+          val = __ldg(Vg + (long long)n * ((long long)g.SH * g.SW * g.SC) + ((long long)(u * g.SW + v) * g.SC + ch));
+      }
+      vraw[0] = val;
+    }
+    uraw = 0.f;
+    if (t < BK * BQT) {
+      const int pix = kb * BK + (t >> 3), qg = q0 + (t & 7);
+      if (pix < prm.K && qg < prm.Q) uraw = __ldg(Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq);
+    }
+  };
+  auto store_tile = [&](int buf, const float (&vraw)[1], float uraw) {
+    Vs[(buf * BK + w) * BPT + lane] = enc_v<true, LM>(__float_as_uint(vraw[0]), prm.m);
+    if (t < BK * BQT) Us[(buf * BK + (t >> 3)) * BQT + (t & 7)] = enc_u<LM>(__float_as_uint(uraw), prm.m);
+  };
+
+  float acc = 0.f;
+  const int nkb = (prm.K + BK - 1) / BK;
+  const bool producer = w < NPROD;
+  const int wc = w - NPROD;  // consumer warp = column
+  if (producer) {
+#pragma unroll
+    for (int j = 0; j < PF; ++j) load_tile(j, vq[j], uq[j]);  // tiles past the end load zeros
+    store_tile(0, vq[0], uq[0]);
+  }
+  __syncthreads();
+  for (int kb0 = 0; kb0 < nkb; kb0 += PF) {
+#pragma unroll
+    for (int j = 0; j < PF; ++j) {
+      const int kb = kb0 + j;
+      if (kb >= nkb) break;
+      const int buf = j & 1;                         // PF is even, so kb & 1 == j & 1
+      // ---- products of this stage: producer warp w takes reduction step w ---------------------
+      if (producer) {
+        load_tile(kb + PF, vq[j], uq[j]);            // slot j is free: tile kb already sits in shared memory
+        const int kk = w;
+        const uint32_t wv = Vs[(buf * BK + kk) * BPT + lane];
+        const uint32_t ci = lm_global(LM) ? (wv & prm.cmask) : ((wv & 0xFFu) | lut_base);
+        const uint32_t cs = (LM == LM_ADD ? wv : (wv & 0xFF800000u)) - 0x3F800000u;
+        const int cn = (int)(0x3F800000u - (wv & 0x7F800000u));
+        const uint4 ua = *reinterpret_cast<const uint4*>(Us + (buf * BK + kk) * BQT);
+        const uint4 ub = *reinterpret_cast<const uint4*>(Us + (buf * BK + kk) * BQT + 4);
+        const uint32_t uq8[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+        for (int r = 0; r < BQT; ++r) {
+          const uint32_t uu = uq8[r];
+          uint32_t bits;
+          if (lm_direct(LM)) {
+            bits = direct_mul_bits<LM == LM_DIRECT_MBM>(wv, uu);
+          } else {
+            const uint32_t pp = uu & 0xFF800000u;
+            const int ee = (int)(uu & 0x7F800000u);
+            uint32_t e;
+            if (LM == LM_ADD) {
+              e = uu & 0x007FFFFFu;
+            } else if (lm_global(LM)) {
+              e = global_entry<LM>(prm.lut_raw, (uu & prm.rmask) | ci, prm.mult, prm.cadj);
+            } else {
+              e = lds_u8((uu & prm.rmask) | ci) * prm.mult;
+            }
+            bits = ee > cn ? e + (pp + cs) : 0u;  // AMsimulator.inl:28: exponent sum <= 127 gives +0
+          }
+          Ps[((buf * BK + kk) * BQT + r) * BPT + lane] = __uint_as_float(bits);
+        }
+        // next stage's operands (loaded PF - 1 stages ago) go to the other buffer, last read before the
+        // previous barrier
+        store_tile(buf ^ 1, vq[(j + 1) % PF], uq[(j + 1) % PF]);
+      }
+      // one barrier per stage; the products buffer alternates, so the producers' next stage does not
+      // disturb the consumers' additions of this one
+      __syncthreads();
+      // ---- consumers: every thread adds its own chain's products in ascending order -------------
+      if (!producer) {
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) acc = __fadd_rn(acc, Ps[((buf * BK + kk) * BQT + wc) * BPT + lane]);
+      }
+    }
+  }
+  const int qg = q0 + wc;
+  if (!producer && pv && qg < prm.Q) prm.O[(long long)pg * prm.o_sp + (long long)qg * prm.o_sq] = acc;
 }
 
 // Sums the split-K partials in ascending split order (fixed order: the result

@@ -470,6 +470,44 @@ def test_balanced_launch_of_the_reduction(ops, oracle, luts, balanced, monkeypat
     assert_bit_equal(yd, oracle.conv2d_fwd(g, x, wt, lut, m), "deterministic mode ignores the balanced launch")
 
 
+@pytest.mark.parametrize("chain", ["1", "0"])
+def test_deterministic_filter_gradient_products_in_parallel_additions_in_order(ops, oracle, luts, chain, monkeypatch, tmp_path):
+    """Few chains, long reduction: a stage's products are computed by all warps in parallel
+    and each thread then adds its own chain's 16 products in ascending order.  Bit-identical
+    to the oracle for every table mode, hazard data included; forced on and off."""
+    monkeypatch.setenv("AMSIM_CHAIN_FGRAD", chain)
+    monkeypatch.setenv("AMSIM_THIN_FGRAD", "1")
+    rng = np.random.default_rng(404)
+    lut9 = rng.integers(0, 256, size=1 << 18, dtype=np.uint8)
+    path9 = str(tmp_path / "RAND_9.bin")
+    lut9.tofile(path9)
+    from oracle.oracle import DIRECT_MBM32, NO_LUT
+    tables = [(lut_path("MBM_7"),) + luts["MBM_7"], (lut_path("MIT_7"),) + luts["MIT_7"], (path9, lut9, 9),
+              ("direct:MBM32", NO_LUT, DIRECT_MBM32)]
+    for (path, lut, m) in tables:
+        for (n, h, w, c, kh, kw, k, s, pad) in [(3, 20, 20, 8, 3, 3, 20, 1, "SAME"), (2, 24, 24, 3, 5, 5, 6, 2, "VALID")]:
+            x, _ = _conv_case(rng, n, h, w, c, kh, kw, k)
+            x.reshape(-1)[rng.choice(x.size, x.size // 50, replace=False)] = rng.choice(
+                np.array([2.5, -3.0, 1e-30, 1e25, 0.0, -0.0], np.float32), x.size // 50)
+            g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+            dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+            dy.reshape(-1)[rng.choice(dy.size, dy.size // 50, replace=False)] = rng.choice(
+                np.array([4.0, -2.0, 1e-28, -1e22, 0.0], np.float32), dy.size // 50)
+            dw = ops.convam_filter_grad((kh, kw, c, k), dev(x), dev(dy), strides=[1, s, s, 1], padding=pad,
+                                        mant_mul_lut=path, deterministic=True).cpu().numpy()
+            with np.errstate(all="ignore"):
+                want = oracle.conv2d_bwd_filter(g, x, dy, lut, m)
+            nan = np.isnan(want)
+            assert np.array_equal(np.isnan(dw), nan)
+            assert_bit_equal(np.where(nan, 0, dw), np.where(nan, 0, want), f"chain={chain} {path[-9:]}")
+    xd = rng.standard_normal((1100, 50)).astype(np.float32)
+    gd = rng.standard_normal((1100, 70)).astype(np.float32)
+    wd = rng.standard_normal((50, 70)).astype(np.float32)
+    lut, m = luts["MBM_7"]
+    _, dwd = ops.denseam_grad(dev(gd), dev(xd), dev(wd), lut_path("MBM_7"), deterministic=True)
+    assert_bit_equal(dwd.cpu().numpy(), oracle.dense_bwd_weight(xd, gd, lut, m), f"dense weight-grad chain={chain}")
+
+
 @pytest.mark.parametrize("thin", [None, "1", "0"])
 def test_deterministic_filter_gradient_thin_and_tiled_kernels(ops, oracle, luts, thin, monkeypatch, tmp_path):
     """Deterministic filter / weight gradients keep one serial chain per output; small
