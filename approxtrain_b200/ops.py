@@ -402,3 +402,28 @@ def matmulam(a: torch.Tensor, b: torch.Tensor, transpose_a: bool = False, transp
     if lead is not None:
         out = out.reshape(*lead, m, n)
     return out
+
+
+def _install_nvtx_ranges() -> None:
+    """With AMSIM_NVTX set in the environment every op call is bracketed by an NVTX range
+    named after the op and its output shape, so a timeline profiler shows the ops by name
+    (the reference has no tracing beyond per-batch wall-clock prints, profile/profile_lut.py:81-106)."""
+    import functools
+    import os
+    if not os.environ.get("AMSIM_NVTX"):
+        return
+    g = globals()
+    for name in ("am_multiply", "convam", "convam_bias_act", "denseam_bias_act", "convam_input_grad",
+                 "convam_filter_grad", "denseam", "denseam_grad", "matmulam"):
+        fn = g[name]
+
+        def wrapped(*a, __fn=fn, __name=name, **k):
+            torch.cuda.nvtx.range_push("amsim." + __name)
+            try:
+                return __fn(*a, **k)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        g[name] = functools.wraps(fn)(wrapped)
+
+
+_install_nvtx_ranges()

@@ -1040,3 +1040,24 @@ def test_plain_c_program_over_the_abi():
         out = subprocess.run([exe, lut_path(name)], capture_output=True, text=True, timeout=300)
         assert out.returncode == 0, out.stderr[-2000:]
         assert "abi_driver ok" in out.stdout
+
+
+@pytest.mark.parametrize("name", ["MBM_7", "MIT_7"])
+def test_reference_gemm_known_inputs(ops, oracle, luts, name):
+    """The reference's own GEMM test case (test/test_gemm.cu:10-15,45-67): A is 800 x 1600 with
+    A[i][j] = i + j, B is 1600 x 800 with B[i][j] = i - j.  Its stored outputs are missing from
+    the reference checkout, so the oracle's chain stands in for them: deterministic mode equals
+    it bit for bit, fast mode within the bar (max-abs reported on failure)."""
+    lut, m = luts[name]
+    i, j = np.meshgrid(np.arange(800, dtype=np.float32), np.arange(1600, dtype=np.float32), indexing="ij")
+    a = (i + j).astype(np.float32)
+    i, j = np.meshgrid(np.arange(1600, dtype=np.float32), np.arange(800, dtype=np.float32), indexing="ij")
+    b = (i - j).astype(np.float32)
+    want = oracle.matmul(a, b, lut, m)
+    got = ops.matmulam(dev(a), dev(b), mant_mul_lut=lut_path(name), deterministic=True).cpu().numpy()
+    assert_bit_equal(got, want, f"reference GEMM case, deterministic, {name}")
+    fast = ops.matmulam(dev(a), dev(b), mant_mul_lut=lut_path(name)).cpu().numpy()
+    assert_close(fast, want, f"reference GEMM case, fast, {name}")
+    # the dense entry points compute the same product
+    y = ops.denseam(dev(a), dev(b), lut_path(name), deterministic=True).cpu().numpy()
+    assert_bit_equal(y, want, f"reference GEMM case through Denseam, {name}")

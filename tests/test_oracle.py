@@ -304,3 +304,20 @@ def test_direct_32bit_models_match_reference(oracle, name):
     want = ref.direct_mul_bits_array(at, bt, m)
     got = oracle.mul(at.view(np.float32), bt.view(np.float32), NO_LUT, m).view(np.uint32)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("name,digest,err", [("MBM_7", "e50d824f5fb99916", 0.02), ("MIT_7", "b29086e212f1ebda", 0.05),
+                                             ("ACC_7", "943976896378e5ff", 0.01)])
+def test_reference_gemm_known_inputs_checksum(oracle, luts, name, digest, err):
+    """The reference's GEMM test case (test/test_gemm.cu:10-15,45-67: A[i][j] = i + j, 800 x 1600;
+    B[i][j] = i - j, 1600 x 800).  Its stored outputs are missing from the reference checkout;
+    the oracle's result is frozen here by checksum and bounded against the exact product."""
+    lut, m = luts[name]
+    i, j = np.meshgrid(np.arange(800, dtype=np.float32), np.arange(1600, dtype=np.float32), indexing="ij")
+    a = (i + j).astype(np.float32)
+    i, j = np.meshgrid(np.arange(1600, dtype=np.float32), np.arange(800, dtype=np.float32), indexing="ij")
+    b = (i - j).astype(np.float32)
+    c = oracle.matmul(a, b, lut, m)
+    assert hashlib.sha256(c.tobytes()).hexdigest()[:16] == digest
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.abs(c - exact).max() / np.abs(exact).max() < err
