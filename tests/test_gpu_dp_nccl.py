@@ -1,0 +1,75 @@
+"""Data-parallel training with the AM ops on two GPUs (NCCL): a batch sharded over
+two ranks must give the update of the full batch on one GPU, within the FP32
+reduction-order tolerance, for a network without batch statistics (LeNet-300-100 with
+denseam layers).  Skipped where fewer than two GPUs are visible."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import lut_path
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _data():
+    g = torch.Generator().manual_seed(3)
+    return torch.rand(64, 784, generator=g), torch.randint(0, 10, (64,), generator=g)
+
+
+def _net(dev):
+    from approxtrain_b200.nets import LeNet300100
+    torch.manual_seed(0)
+    return LeNet300100(lut_path("MBM_7")).to(dev)
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    from approxtrain_b200.dp import DataParallelSGD
+    dev = torch.device("cuda", rank)
+    net = _net(dev)
+    tr = DataParallelSGD(net, lr=0.05)
+    x, y = _data()
+    n = x.shape[0] // world
+    xs, ys = x[rank * n:(rank + 1) * n].to(dev), y[rank * n:(rank + 1) * n].to(dev)
+    for _ in range(2):
+        tr.step(lambda: torch.nn.functional.cross_entropy(net(xs), ys))
+    torch.cuda.synchronize()
+    torch.save([p.detach().cpu() for p in net.parameters()], os.path.join(out, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpus_give_the_full_batch_update(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    r0 = torch.load(tmp_path / "rank0.pt")
+    r1 = torch.load(tmp_path / "rank1.pt")
+    for a, b in zip(r0, r1):
+        assert torch.equal(a, b), "replicas diverged"
+    # one GPU, whole batch, plain SGD on the mean loss
+    from approxtrain_b200.dp import DataParallelSGD
+    dev = torch.device("cuda", 0)
+    net = _net(dev)
+    tr = DataParallelSGD(net, lr=0.05)
+    x, y = _data()
+    x, y = x.to(dev), y.to(dev)
+    for _ in range(2):
+        tr.step(lambda: torch.nn.functional.cross_entropy(net(x), y))
+    for a, p in zip(r0, net.parameters()):
+        assert torch.allclose(a, p.detach().cpu(), atol=1e-6, rtol=1e-4)
