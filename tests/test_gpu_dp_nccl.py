@@ -1,7 +1,8 @@
 """Data-parallel training with the AM ops on two GPUs (NCCL): a batch sharded over
 two ranks must give the update of the full batch on one GPU, within the FP32
-reduction-order tolerance, for a network without batch statistics (LeNet-300-100 with
-denseam layers).  Skipped where fewer than two GPUs are visible."""
+reduction-order tolerance, for the networks without batch statistics: LeNet-300-100
+(denseam layers) and LeNet-5 (AMConv2D filter gradients cross the all-reduce too).
+Skipped where fewer than two GPUs are visible."""
 import os
 import socket
 
@@ -23,27 +24,30 @@ def _free_port():
     return p
 
 
-def _data():
+def _data(which):
     g = torch.Generator().manual_seed(3)
-    return torch.rand(64, 784, generator=g), torch.randint(0, 10, (64,), generator=g)
+    shape = (64, 784) if which == "lenet300100" else (64, 28, 28, 1)
+    return torch.rand(*shape, generator=g), torch.randint(0, 10, (64,), generator=g)
 
 
-def _net(dev):
-    from approxtrain_b200.nets import LeNet300100
+def _net(which, dev):
+    from approxtrain_b200.nets import LeNet5, LeNet300100
     torch.manual_seed(0)
-    return LeNet300100(lut_path("MBM_7")).to(dev)
+    if which == "lenet300100":
+        return LeNet300100(lut_path("MBM_7")).to(dev)
+    return LeNet5(lut_path("MIT_7")).to(dev)
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, which):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world)
     from approxtrain_b200.dp import DataParallelSGD
     dev = torch.device("cuda", rank)
-    net = _net(dev)
+    net = _net(which, dev)
     tr = DataParallelSGD(net, lr=0.05)
-    x, y = _data()
+    x, y = _data(which)
     n = x.shape[0] // world
     xs, ys = x[rank * n:(rank + 1) * n].to(dev), y[rank * n:(rank + 1) * n].to(dev)
     for _ in range(2):
@@ -54,10 +58,11 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_two_gpus_give_the_full_batch_update(tmp_path):
+@pytest.mark.parametrize("which", ["lenet300100", "lenet5"])
+def test_two_gpus_give_the_full_batch_update(tmp_path, which):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), which), nprocs=2, join=True)
     r0 = torch.load(tmp_path / "rank0.pt")
     r1 = torch.load(tmp_path / "rank1.pt")
     for a, b in zip(r0, r1):
@@ -65,11 +70,14 @@ def test_two_gpus_give_the_full_batch_update(tmp_path):
     # one GPU, whole batch, plain SGD on the mean loss
     from approxtrain_b200.dp import DataParallelSGD
     dev = torch.device("cuda", 0)
-    net = _net(dev)
+    net = _net(which, dev)
     tr = DataParallelSGD(net, lr=0.05)
-    x, y = _data()
+    x, y = _data(which)
     x, y = x.to(dev), y.to(dev)
     for _ in range(2):
         tr.step(lambda: torch.nn.functional.cross_entropy(net(x), y))
+    worst = 0.0
     for a, p in zip(r0, net.parameters()):
+        worst = max(worst, float((a - p.detach().cpu()).abs().max()))
         assert torch.allclose(a, p.detach().cpu(), atol=1e-6, rtol=1e-4)
+    print(f"{which}: replicas identical on 2 GPUs; max |sharded - full batch| over all parameters {worst:.3e}")
