@@ -11,7 +11,7 @@ import subprocess
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libamsim.so")
 SOURCES = [os.path.join(_PKG, "csrc", "amsim.cu")]
-HEADERS = [os.path.join(_PKG, "csrc", "amsim_kernels.cuh"),
+HEADERS = [os.path.join(_PKG, "csrc", "amsim_kernels.cuh"), os.path.join(_PKG, "csrc", "amsim_wide.cuh"),
            os.path.join(os.path.dirname(_PKG), "include", "amsim.h")]
 
 NVCC_FLAGS = [

@@ -22,6 +22,7 @@
 #define AMSIM_CTAS1 3
 #endif
 #include "amsim_kernels.cuh"
+#include "amsim_wide.cuh"
 
 #include <atomic>
 
@@ -49,6 +50,77 @@ int fail(int code, const char* fmt, ...) {
     if (e_ != cudaSuccess) return fail(AMSIM_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
   } while (0)
 
+// Debug switches.  The environment is read ONCE, when the first entry point needs a switch (or when
+// amsim_debug_reload_env is called), never on the launch path: a *_workspace query and the launch
+// that follows it always see the same plan.  -1 = not set (the library chooses per shape).
+struct Switches {
+  int balanced = -1;        // AMSIM_BALANCED=0/1        balanced launch of the gather kernels
+  int force_ksplit = -1;    // AMSIM_FORCE_KSPLIT=n      cluster size of the cluster-split launch
+  int no_qsplit = 0;        // AMSIM_NO_QSPLIT=1         narrow outputs on plain 64-column tiles
+  int no_uvec = 0;          // AMSIM_NO_UVEC=1           scalar staging of the uniform operand
+  int no_wgrad_swap = 0;    // AMSIM_NO_WGRAD_SWAP=1     GEMM-shaped weight gradients keep their operand roles
+  int thin_fgrad = -1;      // AMSIM_THIN_FGRAD=0/1      deterministic filter gradient: tiled / thin kernel
+  int thin_tq = -1;         // AMSIM_THIN_TQ=1/2/4       chains per thread of the thin kernel
+  int thin_narrow = 0;      // AMSIM_THIN_NARROW=1       4 instead of 16 warps per CTA in the thin kernel
+  int chain_fgrad = -1;     // AMSIM_CHAIN_FGRAD=0/1     deterministic filter gradient: products-in-parallel kernel
+  int thin_fast = -1;       // AMSIM_THIN_FAST=0/1       fast filter gradient of tiny outputs
+  int exact_only = 0;       // AMSIM_EXACT_ONLY=1        deterministic kernels never use the fast arithmetic
+  int no_additive = 0;      // AMSIM_NO_ADDITIVE=1       additive tables are looked up like any other (at lut_open)
+  int wide = -1;            // AMSIM_WIDE=0/1            16 x 8 register-tile kernels: never / whenever eligible
+  int wide_balanced = -1;   // AMSIM_WIDE_BALANCED=0/1   their balanced launch
+};
+Switches g_sw;
+std::once_flag g_sw_once;
+
+void load_switches() {
+  Switches w;
+  auto tri = [](const char* name, int& v) {
+    if (const char* e = getenv(name)) v = atoi(e);
+  };
+  auto flag = [](const char* name, int& v) { v = getenv(name) != nullptr; };
+  tri("AMSIM_BALANCED", w.balanced);
+  tri("AMSIM_FORCE_KSPLIT", w.force_ksplit);
+  flag("AMSIM_NO_QSPLIT", w.no_qsplit);
+  flag("AMSIM_NO_UVEC", w.no_uvec);
+  flag("AMSIM_NO_WGRAD_SWAP", w.no_wgrad_swap);
+  tri("AMSIM_THIN_FGRAD", w.thin_fgrad);
+  tri("AMSIM_THIN_TQ", w.thin_tq);
+  flag("AMSIM_THIN_NARROW", w.thin_narrow);
+  tri("AMSIM_CHAIN_FGRAD", w.chain_fgrad);
+  tri("AMSIM_THIN_FAST", w.thin_fast);
+  flag("AMSIM_EXACT_ONLY", w.exact_only);
+  flag("AMSIM_NO_ADDITIVE", w.no_additive);
+  tri("AMSIM_WIDE", w.wide);
+  tri("AMSIM_WIDE_BALANCED", w.wide_balanced);
+  g_sw = w;
+}
+
+const Switches& sw() {
+  std::call_once(g_sw_once, load_switches);
+  return g_sw;
+}
+
+// Multiprocessors of a device, looked up once per device.
+int sm_count(int device) {
+  static std::mutex mu;
+  static std::map<int, int> known;
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = known.find(device);
+  if (it != known.end()) return it->second;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+    (void)cudaGetLastError();
+    return 148;  // B200; only reached when the attribute query itself fails
+  }
+  known[device] = sms;
+  return sms;
+}
+
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) (void)cudaGetLastError();
+  return dev;
+}
 
 }  // namespace
 
@@ -153,7 +225,7 @@ int upload_lut(const uint8_t* bytes, int m, int device, amsim_lut** out) {
       }
     // Mitchell-type tables: (carry << m) + mantissa == i + j everywhere, i.e. the multiplier adds the
     // operands' truncated mantissa fields.  The kernels then skip the table (bit-identical result).
-    h->additive = additive && !getenv("AMSIM_NO_ADDITIVE");
+    h->additive = additive && !sw().no_additive;
     e = cudaMalloc(&h->d_canon, h->enc_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&h->d_trans, h->enc_bytes);
     if (e == cudaSuccess) e = cudaMemcpy(h->d_canon, canon.data(), h->enc_bytes, cudaMemcpyHostToDevice);
@@ -222,7 +294,7 @@ void fill_lut(Params& p, const amsim_lut* lut, bool v_is_first_operand) {
                : lut->m > 7 ? LM_GLOBAL : (lut->additive ? LM_ADD : LM_SMEM);
   p.lut_raw = v_is_first_operand ? lut->d_raw_t : lut->d_raw;
   p.v_first = v_is_first_operand ? 1 : 0;
-  p.exact_only = getenv("AMSIM_EXACT_ONLY") != nullptr;
+  p.exact_only = sw().exact_only;
   uint32_t al = 16;
   while (al < (uint32_t)lut->enc_bytes) al <<= 1;
   p.lut_align = al;  // m > 7: no table in shared memory (enc_bytes = 0)
@@ -258,22 +330,103 @@ int resident_slots(Kern kern, size_t smem, int device, int* out) {
   return AMSIM_OK;
 }
 
-// Stream-ordered scratch for the balanced launch: the pool keeps freed blocks, so after the
-// first call this neither synchronises nor reaches the driver's allocator.
+// Stream-ordered scratch for the balanced launch, from a memory pool this library creates per
+// device (the process-wide default pool is left as the host framework configured it).  The pool
+// keeps its freed blocks, so after the first call this neither synchronises nor reaches the
+// driver's allocator.
 int scratch_alloc(cudaStream_t st, int device, size_t bytes, float** out) {
   static std::mutex mu;
-  static std::set<int> tuned;
+  static std::map<int, cudaMemPool_t> pools;
+  cudaMemPool_t pool = nullptr;
   {
     std::lock_guard<std::mutex> lk(mu);
-    if (!tuned.count(device)) {
-      cudaMemPool_t pool;
-      CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, device));
+    auto it = pools.find(device);
+    if (it == pools.end()) {
+      cudaMemPoolProps props;
+      memset(&props, 0, sizeof(props));
+      props.allocType = cudaMemAllocationTypePinned;
+      props.handleTypes = cudaMemHandleTypeNone;
+      props.location.type = cudaMemLocationTypeDevice;
+      props.location.id = device;
+      CUDA_TRY(cudaMemPoolCreate(&pool, &props));
       uint64_t keep = ~0ull;
       CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
-      tuned.insert(device);
+      pools[device] = pool;
+    } else {
+      pool = it->second;
     }
   }
-  CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(out), bytes, st));
+  CUDA_TRY(cudaMallocFromPoolAsync(reinterpret_cast<void**>(out), bytes, pool, st));
+  return AMSIM_OK;
+}
+
+// ---- 16 x 8 register-tile kernels (amsim_wide.cuh) ------------------------------------------------
+// Rate of the wide kernels relative to the 16 x 4 kernels (time per padded product), used to weigh
+// their larger tile padding against their cheaper operand fetch.
+constexpr double kWideRate = 0.93;
+
+template <int LM>
+int launch_wide_gather(cudaStream_t st, Params& p, int batch, int device, bool* taken) {
+  *taken = false;
+  if (sw().wide == 0 || p.Q <= 32) return AMSIM_OK;
+  const int nkb = (p.K + BK - 1) / BK;
+  const int ptiles = (p.P + WBP - 1) / WBP, qtiles = (p.Q + BQ - 1) / BQ;
+  const long long ctas = (long long)ptiles * qtiles * batch;
+  if (sw().wide < 0) {
+    // worth it when the problem fills the device a few times over and the 256-row tiles do not
+    // pad away what the cheaper operand fetch gains
+    const long long rows_w = (long long)ptiles * WBP, rows_n = (long long)((p.P + 127) / 128) * 128;
+    if ((double)rows_w * kWideRate >= (double)rows_n) return AMSIM_OK;
+    if (ctas * nkb < 8ll * 2 * sm_count(device)) return AMSIM_OK;
+  }
+  p.tile_bytes = wide_tile_bytes(0);
+  const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
+  int rc = ensure_smem(wide_gather<LM, GM_BALANCED>, smem, device);
+  if (rc) return rc;
+  rc = ensure_smem(wide_gather<LM, GM_PLAIN>, smem, device);
+  if (rc) return rc;
+  int slots = 0;
+  rc = resident_slots(wide_gather<LM, GM_BALANCED>, smem, device, &slots);
+  if (rc) return rc;
+  const long long iters = ctas * nkb;
+  const long long waves = slots > 0 ? (ctas + slots - 1) / slots : 1;
+  const double fill = slots > 0 ? (double)ctas / (double)(waves * slots) : 1.0;
+  long long grid = slots;
+  if (iters / (grid > 0 ? grid : 1) < 2) grid = iters / 2;
+  int balanced = fill < 0.93 && grid >= 2 && nkb >= 2;
+  if (sw().wide_balanced >= 0) balanced = sw().wide_balanced != 0 && grid >= 1;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  CUDA_TRY(cudaStreamIsCapturing(st, &cap));
+  *taken = true;
+  if (balanced && cap == cudaStreamCaptureStatusNone && slots > 0) {
+    p.sk_iters = iters;
+    p.sk_ptiles = ptiles;
+    p.sk_qtiles = qtiles;
+    p.sk_grid = (int)grid;
+    const size_t slot_bytes = (size_t)grid * 2 * W_ACC * sizeof(float);
+    const size_t bytes = slot_bytes + (size_t)ctas * sizeof(int);
+    rc = scratch_alloc(st, device, bytes, &p.ws);
+    if (rc == AMSIM_OK) {
+      p.sk_count = reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) + slot_bytes);
+      cudaError_t e1 = cudaMemsetAsync(p.sk_count, 0, (size_t)ctas * sizeof(int), st);
+      if (e1 == cudaSuccess) {
+        AMSIM_COUNT_LAUNCH();
+        wide_gather<LM, GM_BALANCED><<<dim3((unsigned)grid), WNT, smem, st>>>(p);
+        e1 = cudaGetLastError();
+      }
+      cudaError_t e2 = cudaFreeAsync(p.ws, st);
+      p.ws = nullptr;
+      p.sk_count = nullptr;
+      CUDA_TRY(e1);
+      CUDA_TRY(e2);
+      return AMSIM_OK;
+    }
+    (void)cudaGetLastError();  // no scratch to be had: the plain grid needs none
+    p.ws = nullptr;
+  }
+  AMSIM_COUNT_LAUNCH();
+  wide_gather<LM, GM_PLAIN><<<dim3(ptiles, qtiles, batch), WNT, smem, st>>>(p);
+  CUDA_TRY(cudaGetLastError());
   return AMSIM_OK;
 }
 
@@ -287,11 +440,19 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   p.tile_bytes = L::TILE_BYTES;
   const size_t smem_plain = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
 
+  // Fast mode, large launches with 128-bit gathers: the 16 x 8 register-tile kernel.
+  if constexpr (!EXACT && VEC && (LM == LM_SMEM || LM == LM_ADD)) {
+    bool taken = false;
+    int rc = launch_wide_gather<LM>(st, p, batch, device, &taken);
+    if (rc || taken) return rc;
+    p.tile_bytes = L::TILE_BYTES;
+  }
+
   // Fast mode, narrow outputs (at most 32 columns: first-layer input gradients, small heads, LeNet-5's
   // convolutions): 2 or 4 warps share each 16-column group and split the reduction steps.
   if constexpr (!EXACT && !lm_direct(LM)) {
     const int qs = p.Q <= 16 ? 4 : p.Q <= 32 ? 2 : 1;
-    if (qs > 1 && nkb >= 2 && !getenv("AMSIM_NO_QSPLIT")) {
+    if (qs > 1 && nkb >= 2 && !sw().no_qsplit) {
       const int qt = (p.Q + BQ / qs - 1) / (BQ / qs);
       if (qs == 4) {
         int rc = ensure_smem(gather_gemm<1, EXACT, VEC, GM_PLAIN, LM, 4>, smem_plain, device);
@@ -331,7 +492,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
     // measured: pays when the plain grid is at most two waves with a last wave under ~93 % full
     // (one wave at 88 %: -7 %); with more waves the plain grid's tail is already short
     int mode = waves <= 2 && fill < 0.93 && grid >= 2 && nkb >= 2;
-    if (const char* f = getenv("AMSIM_BALANCED")) mode = atoi(f) != 0 && grid >= 1;
+    if (sw().balanced >= 0) mode = sw().balanced != 0 && grid >= 1;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     CUDA_TRY(cudaStreamIsCapturing(st, &cap));
     if (mode && cap == cudaStreamCaptureStatusNone && slots > 0) {
@@ -367,9 +528,9 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   // shares each tile's reduction when the tiles alone cannot fill the resident CTA slots.
   int ksplit = 1;
   if (!EXACT && !lm_global(LM)) {
-    const int slots = 148 * AMSIM_CTAS1;
+    const int slots = sm_count(device) * AMSIM_CTAS1;
     while (ksplit < 8 && ctas * (ksplit * 2) <= slots && nkb / (ksplit * 2) >= 2) ksplit *= 2;
-    if (const char* f = getenv("AMSIM_FORCE_KSPLIT")) ksplit = atoi(f) > 0 ? atoi(f) : 1;
+    if (sw().force_ksplit >= 0) ksplit = sw().force_ksplit > 0 ? sw().force_ksplit : 1;
   }
   p.ksplit = ksplit;
   if (ksplit > 1 && L::EXCHANGE_BYTES > p.tile_bytes) p.tile_bytes = L::EXCHANGE_BYTES;
@@ -410,7 +571,7 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
   // group inside one tap: along q (weights of a forward convolution / dense layer / matmul B),
   // or along k (flipped filter of an input gradient, transposed matmul B)
   p.u_vec = 0;
-  if (aligned16(p.U) && p.u_bs % 4 == 0 && p.u_tap % 4 == 0 && !getenv("AMSIM_NO_UVEC")) {
+  if (aligned16(p.U) && p.u_bs % 4 == 0 && p.u_tap % 4 == 0 && !sw().no_uvec) {
     if (p.u_sq == 1 && p.u_sk % 4 == 0 && p.Q % 4 == 0) p.u_vec = 1;
     else if (p.u_sk == 1 && p.u_sq % 4 == 0 && p.g.SC % 4 == 0) p.u_vec = 2;
   }
@@ -432,18 +593,36 @@ int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device)
 }
 
 struct FgradPlan {
-  int wp, splits, k_chunk;
+  int np;  // rows per lane of the tile: 0 = the 128-row kernels, 8 / 9 = wide_fgrad
+  int splits, k_chunk;
   int thin, tq;  // one-to-four-chains-per-thread kernel instead of the 128 x 64 tiles
   size_t ws_bytes;
 };
 
+// Rows per lane a fast-mode filter gradient of P x Q outputs would take if its operands allow the
+// wide kernel (128-bit gathers, table in shared memory or additive): the tile height with the least
+// padded work, weighted by the kernels' rates.  0 = the 128-row kernel.
+int pick_fgrad_rows(int P, int Q, int K, int sms) {
+  if (sw().wide == 0) return 0;
+  auto padded = [&](int bp) { return (double)((P + bp - 1) / bp) * bp; };
+  int best = 8;
+  double cost = padded(256);
+  if (padded(288) < cost) { best = 9; cost = padded(288); }
+  if (sw().wide > 0) return best;
+  if (cost * kWideRate >= padded(128)) return 0;
+  const long long tiles = (long long)((P + 32 * best - 1) / (32 * best)) * ((Q + BQ - 1) / BQ);
+  if (tiles * ((K + BK - 1) / BK) < 8ll * 2 * sms) return 0;  // too small to fill the device a few times over
+  return best;
+}
+
 // How a filter / weight gradient of P x Q outputs over a reduction of K runs.  Depends on the
-// dimensions, the mode and the environment only, so the *_workspace functions and the launch agree.
-FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
+// dimensions, the mode, the device's multiprocessor count and the debug switches (read once) only,
+// so the *_workspace functions and the launch agree.
+FgradPlan plan_fgrad(int P, int Q, int K, bool exact, int np, int sms) {
   FgradPlan f;
-  f.wp = 1;  // 128-row tiles: 3 CTAs of 4 warps per SM without register spills
-  const int bp = f.wp * 128;
-  const int slots = 148 * (f.wp == 1 ? 3 : 2);  // resident CTAs on the whole GPU
+  f.np = exact ? 0 : np;
+  const int bp = f.np ? 32 * f.np : 128;
+  const int slots = sms * (f.np ? 2 : AMSIM_CTAS1);  // resident CTAs on the whole GPU (launch bounds of the kernels)
   const long long tiles = (long long)((P + bp - 1) / bp) * ((Q + BQ - 1) / BQ);
   const long long chains = (long long)P * Q;
   f.thin = 0;
@@ -453,18 +632,18 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
     // Deterministic mode cannot split a reduction; when the 128 x 64 tiles would fill less than
     // half of the resident CTA slots, threads take fewer chains each so the whole device works.
     f.thin = tiles * 2 < slots;
-    if (const char* e = getenv("AMSIM_THIN_FGRAD")) f.thin = atoi(e) != 0;
-    f.tq = chains >= 4ll * 32 * 4 * 148 * 2 ? 4 : chains >= 2ll * 32 * 4 * 148 * 2 ? 2 : 1;
-    if (const char* e = getenv("AMSIM_THIN_TQ")) f.tq = atoi(e);
+    if (sw().thin_fgrad >= 0) f.thin = sw().thin_fgrad != 0;
+    f.tq = chains >= 4ll * 32 * 4 * sms * 2 ? 4 : chains >= 2ll * 32 * 4 * sms * 2 ? 2 : 1;
+    if (sw().thin_tq > 0) f.tq = sw().thin_tq;
   } else if (tiles > 0) {
     // Fast mode, tiny outputs (LeNet-5's 5x5x1x6 filter: 150 of a tile's 8192 outputs): one chain per
     // thread over a slice of the reduction wastes nothing on padding; many slices, summed in order.
-    f.thin = (double)chains < 0.2 * (double)(tiles * bp * BQ);
-    if (const char* e = getenv("AMSIM_THIN_FAST")) f.thin = atoi(e) != 0;
+    f.thin = !f.np && (double)chains < 0.2 * (double)(tiles * bp * BQ);
+    if (sw().thin_fast >= 0 && !f.np) f.thin = sw().thin_fast != 0;
     if (f.thin) {
       const int nw = (Q + f.tq - 1) / f.tq > 4 ? 16 : 4;
       const long long ctas = (long long)((P + 31) / 32) * ((Q + nw * f.tq - 1) / (nw * f.tq));
-      splits = (int)(4 * 148 / ctas);
+      splits = (int)(4 * sms / ctas);
       const int max_splits = (K + 2 * BK - 1) / (2 * BK);  // at least 2 stages per split
       if (splits > max_splits) splits = max_splits;
     } else {
@@ -483,6 +662,37 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact) {
   f.ws_bytes = f.splits > 1 ? (size_t)f.splits * P * Q * sizeof(float) : 0;
   return f;
 }
+
+// Workspace that covers whichever plan the launch takes (the wide kernel needs operands the
+// query cannot see: 16-byte aligned tensors, a table in shared memory).
+size_t fgrad_workspace(int P, int Q, int K, bool exact, int sms) {
+  size_t need = plan_fgrad(P, Q, K, exact, 0, sms).ws_bytes;
+  if (!exact) {
+    const int np = pick_fgrad_rows(P, Q, K, sms);
+    if (np) need = std::max(need, plan_fgrad(P, Q, K, false, np, sms).ws_bytes);
+  }
+  return need;
+}
+
+template <int LM, int NP>
+int launch_wide_fgrad_t(cudaStream_t st, Params& p, int device) {
+  p.tile_bytes = wide_tile_bytes(NP);
+  const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
+  int rc = ensure_smem(wide_fgrad<LM, NP>, smem, device);
+  if (rc) return rc;
+  dim3 grid((p.P + 32 * NP - 1) / (32 * NP), (p.Q + BQ - 1) / BQ, p.splits);
+  AMSIM_COUNT_LAUNCH();
+  wide_fgrad<LM, NP><<<grid, WNT, smem, st>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  if (p.splits > 1) {
+    const long long n = (long long)p.P * p.Q;
+    AMSIM_COUNT_LAUNCH();
+    reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq);
+    CUDA_TRY(cudaGetLastError());
+  }
+  return AMSIM_OK;
+}
+
 template <bool EXACT, bool VEC, int LM>
 int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   using L = SmemLayout<1>;
@@ -536,7 +746,7 @@ int launch_fgrad_chain(cudaStream_t st, Params& p, int device) {
 template <int LM>
 int launch_fgrad_thin(cudaStream_t st, Params& p, int tq, bool flush, int device) {
   // 16 warps per CTA share one staged V tile when the output is wide enough to use them
-  const bool wide = (p.Q + tq - 1) / tq > 4 && !getenv("AMSIM_THIN_NARROW");
+  const bool wide = (p.Q + tq - 1) / tq > 4 && !sw().thin_narrow;
   if (flush) {  // fast mode: tiny outputs only, one chain per thread
     if constexpr (lm_direct(LM)) return fail(AMSIM_ERR_UNSUPPORTED, "direct models run in ordered mode");
     else return wide ? launch_fgrad_thin_t<1, 16, LM, true>(st, p, device) : launch_fgrad_thin_t<1, 4, LM, true>(st, p, device);
@@ -549,7 +759,13 @@ int launch_fgrad_thin(cudaStream_t st, Params& p, int tq, bool flush, int device
 int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_bytes, int device) {
   if (p.P <= 0 || p.Q <= 0) return AMSIM_OK;
   if (lm_direct(p.lut_mode)) exact = true;  // one kernel flavour for the direct models: ordered chains
-  const FgradPlan f = plan_fgrad(p.P, p.Q, p.K, exact);
+  const int sms = sm_count(device);
+  const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
+  FgradPlan f = plan_fgrad(p.P, p.Q, p.K, exact, 0, sms);
+  if (!exact && !f.thin && vec && (p.lut_mode == LM_SMEM || p.lut_mode == LM_ADD)) {
+    const int np = pick_fgrad_rows(p.P, p.Q, p.K, sms);
+    if (np) f = plan_fgrad(p.P, p.Q, p.K, false, np, sms);
+  }
   if (f.ws_bytes > 0) {
     if (!ws || ws_bytes < f.ws_bytes)
       return fail(AMSIM_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", f.ws_bytes, ws ? ws_bytes : (size_t)0);
@@ -558,13 +774,19 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   p.splits = f.splits;
   p.k_chunk = f.k_chunk;
   p.ws = static_cast<float*>(ws);
+  if (f.np) {
+    p.u_vec = aligned16(p.U) && p.u_sq == 1 && p.u_sk % 4 == 0 && p.Q % 4 == 0 && !sw().no_uvec;
+    if (p.lut_mode == LM_ADD)
+      return f.np == 9 ? launch_wide_fgrad_t<LM_ADD, 9>(st, p, device) : launch_wide_fgrad_t<LM_ADD, 8>(st, p, device);
+    return f.np == 9 ? launch_wide_fgrad_t<LM_SMEM, 9>(st, p, device) : launch_wide_fgrad_t<LM_SMEM, 8>(st, p, device);
+  }
   if (f.thin) {
     {
       const int tq = f.tq;
       const bool flush = !exact;
       // deterministic, few chains and a long reduction: products in parallel, additions in order
-      int chain = exact && (long long)p.P * p.Q <= 2ll * 148 * 256 && p.K >= 64 * BK;
-      if (const char* e = getenv("AMSIM_CHAIN_FGRAD")) chain = exact && atoi(e) != 0;
+      int chain = exact && (long long)p.P * p.Q <= 2ll * sms * 256 && p.K >= 64 * BK;
+      if (sw().chain_fgrad >= 0) chain = exact && sw().chain_fgrad != 0;
       if (chain) {
         if (p.lut_mode == LM_DIRECT_MBM) return launch_fgrad_chain<LM_DIRECT_MBM>(st, p, device);
         if (p.lut_mode == LM_DIRECT_MIT) return launch_fgrad_chain<LM_DIRECT_MIT>(st, p, device);
@@ -581,8 +803,7 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
       return launch_fgrad_thin<LM_SMEM>(st, p, tq, flush, device);
     }
   }
-  const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
-  p.u_vec = aligned16(p.U) && p.u_sq == 1 && p.u_sk % 4 == 0 && p.Q % 4 == 0 && !getenv("AMSIM_NO_UVEC");
+  p.u_vec = aligned16(p.U) && p.u_sq == 1 && p.u_sk % 4 == 0 && p.Q % 4 == 0 && !sw().no_uvec;
 #define AMSIM_GO(EX_, VEC_, LM_) return launch_fgrad_t<EX_, VEC_, LM_>(st, p, device)
 #define AMSIM_GO_LM(LM_)                                                                        \
   do {                                                                                          \
@@ -637,6 +858,11 @@ const char* amsim_last_error(void) { return g_err; }
 const char* amsim_version(void) { return "amsim 0.1 (sm_100a)"; }
 
 unsigned long long amsim_debug_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+void amsim_debug_reload_env(void) {
+  sw();  // make sure the one-time load has happened, then replace its result
+  load_switches();
+}
 
 uint32_t amsim_debug_fastdiv(uint32_t n, uint32_t d) { return fdiv(n, make_fastdiv(d)); }
 
@@ -748,7 +974,8 @@ int amsim_mul(void* stream, const amsim_lut* lut, const float* a, const float* b
   if (n == 0) return AMSIM_OK;
   if (!a || !b || !out) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   size_t blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const size_t cap = (size_t)sm_count(lut->device) * 16;
+  if (blocks > cap) blocks = cap;
   AMSIM_COUNT_LAUNCH();
   mul_elementwise<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, b, out, n, lut->d_raw, lut->m, lut->direct ? lut->direct : lut->wide ? LM_GLOBAL16 : 0);
   CUDA_TRY(cudaGetLastError());
@@ -914,7 +1141,7 @@ int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, c
 // output is written transposed, so every product and every chain is the same.
 static bool wgrad_swap(int in_w, int units) {
   auto padded = [](long long p, long long q) { return ((p + 127) / 128 * 128) * ((q + BQ - 1) / BQ * BQ); };
-  if (getenv("AMSIM_NO_WGRAD_SWAP")) return false;
+  if (sw().no_wgrad_swap) return false;
   return padded(units, in_w) < padded(in_w, units);
 }
 
@@ -936,16 +1163,24 @@ static void setup_wgrad(Params& p, const amsim_lut* lut, const float* x, const f
   fill_lut(p, lut, /*v_is_first_operand=*/!swap);
 }
 
-size_t amsim_conv2d_bwd_filter_workspace(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c,
-                                         int out_h, int out_w, unsigned flags) {
+// Split-K scratch of a filter gradient; 0 for shapes the op itself refuses (check_conv_dims).
+static size_t conv_fgrad_workspace(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
+                                   int out_w, bool det, int sms) {
   if (batch <= 0 || in_c <= 0 || f_h <= 0 || f_w <= 0 || out_c <= 0 || out_h <= 0 || out_w <= 0) return 0;
-  if (flags & AMSIM_INT32) return 0;
-  const bool det = flags & AMSIM_DETERMINISTIC;
-  size_t need = plan_fgrad(f_h * f_w * in_c, out_c, batch * out_h * out_w, det).ws_bytes;
+  const long long rows = (long long)f_h * f_w * in_c, npix = (long long)batch * out_h * out_w;
+  if (rows >= (1ll << 30) || (long long)f_h * f_w * out_c >= (1ll << 30) || npix >= (1ll << 31) - 256) return 0;
+  size_t need = fgrad_workspace((int)rows, out_c, (int)npix, det, sms);
   // a 1x1 stride-1 convolution may run with the operand roles swapped (wgrad_swap): cover both plans
   if (f_h == 1 && f_w == 1 && out_h == in_h && out_w == in_w && wgrad_swap(in_c, out_c))
-    need = std::max(need, plan_fgrad(out_c, in_c, batch * out_h * out_w, det).ws_bytes);
+    need = std::max(need, fgrad_workspace(out_c, in_c, (int)npix, det, sms));
   return need;
+}
+
+size_t amsim_conv2d_bwd_filter_workspace(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c,
+                                         int out_h, int out_w, unsigned flags) {
+  if (flags & AMSIM_INT32) return 0;
+  return conv_fgrad_workspace(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, flags & AMSIM_DETERMINISTIC,
+                              sm_count(current_device()));
 }
 
 int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, const float* dy, float* dw, int batch,
@@ -1014,8 +1249,13 @@ int amsim_conv2d_bwd_filter_static(void* stream, const amsim_lut* lut, const flo
                                    int out_w, int stride_h, int stride_w, int pad_top, int pad_left, unsigned flags) {
   int rc = check_common(lut, flags, true);  // also checks that lut->device is the current device
   if (rc) return rc;
-  const size_t need =
-      amsim_conv2d_bwd_filter_workspace(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, flags);
+  rc = check_conv_dims(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w, stride_h, stride_w, pad_top, pad_left);
+  if (rc) return rc;
+  // the plan the launch will take: direct models always run unsplit (ordered chains), as in launch_fgrad
+  const bool det = (flags & AMSIM_DETERMINISTIC) || lut->direct;
+  const size_t need = (flags & AMSIM_INT32) ? 0
+                                            : conv_fgrad_workspace(batch, in_h, in_w, in_c, f_h, f_w, out_c, out_h, out_w,
+                                                                   det, sm_count(lut->device));
   if (need > (size_t)AMSIM_STATIC_SCRATCH_BYTES)
     return fail(AMSIM_ERR_WORKSPACE,
                 "this shape needs %zu bytes of split-K scratch, the built-in buffer holds %u: "
@@ -1093,8 +1333,9 @@ int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w, co
 size_t amsim_dense_bwd_weight_workspace(int batch, int units, int input_width, unsigned flags) {
   if (batch <= 0 || units <= 0 || input_width <= 0) return 0;
   if (flags & AMSIM_INT32) return 0;
-  if (wgrad_swap(input_width, units)) return plan_fgrad(units, input_width, batch, flags & AMSIM_DETERMINISTIC).ws_bytes;
-  return plan_fgrad(input_width, units, batch, flags & AMSIM_DETERMINISTIC).ws_bytes;
+  const int sms = sm_count(current_device());
+  if (wgrad_swap(input_width, units)) return fgrad_workspace(units, input_width, batch, flags & AMSIM_DETERMINISTIC, sms);
+  return fgrad_workspace(input_width, units, batch, flags & AMSIM_DETERMINISTIC, sms);
 }
 
 int amsim_dense_bwd_weight(void* stream, const amsim_lut* lut, const float* x, const float* g_, float* dw, int batch,

@@ -274,6 +274,13 @@ int amsim_matmul_ex(void* stream, const amsim_lut* lut, const float* a, const fl
  * streams).  For benchmarks that report their launch count; no reference counterpart. */
 unsigned long long amsim_debug_launch_count(void);
 
+/* The debug switches (environment variables AMSIM_*, listed in INTEGRATION.md) are read once,
+ * when an entry point first needs one; they are never read on the launch path, so a *_workspace
+ * query and the launch that follows it see the same plan.  This call re-reads them.  Meant for
+ * tests that change a switch between two calls; not safe against launches running in other
+ * threads.  No reference counterpart. */
+void amsim_debug_reload_env(void);
+
 /* Host-side check of the kernels' constant-divisor arithmetic (no GPU work):
  * returns n / d computed the way the device code does.  For tests. */
 uint32_t amsim_debug_fastdiv(uint32_t n, uint32_t d);

@@ -40,3 +40,25 @@ def rel_l2(a, b) -> float:
     b = np.asarray(b, np.float64)
     den = np.linalg.norm(b.ravel())
     return float(np.linalg.norm((a - b).ravel()) / (den if den > 0 else 1.0))
+
+
+def set_switch(monkeypatch, name: str, value) -> None:
+    """Sets (or, with value None, removes) one of the library's AMSIM_* debug switches for the rest
+    of the test and makes the library re-read its switches (it reads the environment once)."""
+    from approxtrain_b200 import _lib
+    if value is None:
+        monkeypatch.delenv(name, raising=False)
+    else:
+        monkeypatch.setenv(name, str(value))
+    _lib.lib.amsim_debug_reload_env()
+
+
+@pytest.fixture(autouse=True)
+def _restore_switches():
+    """After a test (and after monkeypatch has put the environment back) the library re-reads its switches."""
+    yield
+    try:
+        from approxtrain_b200 import _lib
+    except Exception:
+        return
+    _lib.lib.amsim_debug_reload_env()

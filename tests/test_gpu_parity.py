@@ -9,7 +9,7 @@ import os
 import numpy as np
 import pytest
 
-from conftest import BIG_LUT, GOLDEN, SMALL_LUTS, lut_path, rel_l2
+from conftest import BIG_LUT, GOLDEN, SMALL_LUTS, lut_path, rel_l2, set_switch
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -169,8 +169,8 @@ def test_fast_forward_is_bit_exact_without_zero_operands(ops, oracle, luts, monk
     computes the reference products exactly and, where one warp of one CTA owns an
     output's whole reduction (more than 32 output columns, plain grid), sums them in
     the reference order: VALID padding, N(0,1) data."""
-    monkeypatch.setenv("AMSIM_BALANCED", "0")
-    monkeypatch.setenv("AMSIM_FORCE_KSPLIT", "1")
+    set_switch(monkeypatch, "AMSIM_BALANCED", "0")
+    set_switch(monkeypatch, "AMSIM_FORCE_KSPLIT", "1")
     lut, m = luts["MBM_7"]
     rng = np.random.default_rng(17)
     x = rng.standard_normal((2, 12, 12, 8)).astype(np.float32)
@@ -407,9 +407,9 @@ def test_cluster_split_of_the_reduction(ops, oracle, luts, force, monkeypatch):
     x, wt = _conv_case(rng, 2, 7, 7, 64, 3, 3, 96)          # 98 pixels, 2 channel tiles, K = 576 (36 stages)
     g = oracle.geometry(2, 7, 7, 64, 3, 3, 96, 1, 1, "SAME")
     dy = rng.standard_normal((2, 7, 7, 96)).astype(np.float32)
-    monkeypatch.setenv("AMSIM_BALANCED", "0")  # outside a graph capture the balanced launch would take this shape
+    set_switch(monkeypatch, "AMSIM_BALANCED", "0")  # outside a graph capture the balanced launch would take this shape
     if force is not None:
-        monkeypatch.setenv("AMSIM_FORCE_KSPLIT", force)
+        set_switch(monkeypatch, "AMSIM_FORCE_KSPLIT", force)
     kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=lut_path("MBM_7"))
     y = ops.convam(dev(x), dev(wt), **kw_).cpu().numpy()
     dx = ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_).cpu().numpy()
@@ -429,7 +429,7 @@ def test_balanced_launch_of_the_reduction(ops, oracle, luts, balanced, monkeypat
     parity bar, run-to-run identical, every epilogue (strided output rows of a
     stride-2 input gradient, bias + ReLU, batched matmul) and every table mode."""
     if balanced is not None:
-        monkeypatch.setenv("AMSIM_BALANCED", balanced)
+        set_switch(monkeypatch, "AMSIM_BALANCED", balanced)
     lut, m = luts["MBM_7"]
     p7 = lut_path("MBM_7")
     rng = np.random.default_rng(77)
@@ -475,8 +475,8 @@ def test_deterministic_filter_gradient_products_in_parallel_additions_in_order(o
     """Few chains, long reduction: a stage's products are computed by all warps in parallel
     and each thread then adds its own chain's 16 products in ascending order.  Bit-identical
     to the oracle for every table mode, hazard data included; forced on and off."""
-    monkeypatch.setenv("AMSIM_CHAIN_FGRAD", chain)
-    monkeypatch.setenv("AMSIM_THIN_FGRAD", "1")
+    set_switch(monkeypatch, "AMSIM_CHAIN_FGRAD", chain)
+    set_switch(monkeypatch, "AMSIM_THIN_FGRAD", "1")
     rng = np.random.default_rng(404)
     lut9 = rng.integers(0, 256, size=1 << 18, dtype=np.uint8)
     path9 = str(tmp_path / "RAND_9.bin")
@@ -515,7 +515,7 @@ def test_deterministic_filter_gradient_thin_and_tiled_kernels(ops, oracle, luts,
     64-chain register tile.  Both kernels, forced and as chosen by the library, are
     bit-identical to the oracle for every table mode."""
     if thin is not None:
-        monkeypatch.setenv("AMSIM_THIN_FGRAD", thin)
+        set_switch(monkeypatch, "AMSIM_THIN_FGRAD", thin)
     rng = np.random.default_rng(91)
     lut9 = rng.integers(0, 256, size=1 << 18, dtype=np.uint8)
     path9 = str(tmp_path / "RAND_9.bin")
@@ -794,9 +794,9 @@ def test_additive_table_shortcut_is_bit_identical_to_the_table_path(ops, oracle,
     # a second copy of the file, opened with the shortcut disabled -> table path
     table_copy = str(tmp_path / "MITCOPY_7.bin")
     shutil.copyfile(lut_path("MIT_7"), table_copy)
-    monkeypatch.setenv("AMSIM_NO_ADDITIVE", "1")
+    set_switch(monkeypatch, "AMSIM_NO_ADDITIVE", "1")
     ops.get_lut(table_copy, "cuda")
-    monkeypatch.delenv("AMSIM_NO_ADDITIVE")
+    set_switch(monkeypatch, "AMSIM_NO_ADDITIVE", None)
     for det in (True, False):
         outs = {}
         for tag, path in (("add", lut_path("MIT_7")), ("table", table_copy)):
@@ -872,7 +872,7 @@ def test_weight_gradient_with_swapped_operand_roles(ops, oracle, luts, noswap, m
     one, the table indexed the other way round and the output written transposed: same
     products, same chains.  Deterministic bit-exact, fast within the bar, asymmetric LUT."""
     if noswap:
-        monkeypatch.setenv("AMSIM_NO_WGRAD_SWAP", noswap)
+        set_switch(monkeypatch, "AMSIM_NO_WGRAD_SWAP", noswap)
     rng = np.random.default_rng(64)
     lut = rng.integers(0, 256, size=1 << 10, dtype=np.uint8)   # m = 5, not symmetric
     from approxtrain_b200 import _lib
@@ -909,8 +909,8 @@ def test_deterministic_mode_hazard_stages(ops, oracle, luts, exact_only, monkeyp
     bit-identical to the oracle in all three directions, with the fast arithmetic allowed
     and with it switched off."""
     if exact_only:
-        monkeypatch.setenv("AMSIM_EXACT_ONLY", exact_only)
-    monkeypatch.setenv("AMSIM_THIN_FGRAD", "0")   # the tiled filter-gradient kernel is the one with the two loops
+        set_switch(monkeypatch, "AMSIM_EXACT_ONLY", exact_only)
+    set_switch(monkeypatch, "AMSIM_THIN_FGRAD", "0")   # the tiled filter-gradient kernel is the one with the two loops
     rng = np.random.default_rng(2718)
 
     def spice(a, frac=0.08):
@@ -1001,7 +1001,7 @@ def test_narrow_outputs_share_column_groups_between_warps(ops, oracle, luts, off
     their register tiles are added in warp order.  Fast mode only; same bar, run-to-run identical,
     fused epilogue and strided (stride-phase) outputs included."""
     if off:
-        monkeypatch.setenv("AMSIM_NO_QSPLIT", off)
+        set_switch(monkeypatch, "AMSIM_NO_QSPLIT", off)
     rng = np.random.default_rng(321)
     for name in ("MBM_7", "MIT_7"):
         lut, m = luts[name]

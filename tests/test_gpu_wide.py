@@ -1,0 +1,161 @@
+"""GPU parity of the 16 x 8 register-tile kernels (wide_gather / wide_fgrad).
+
+By default these kernels only take launches large enough to fill the device a few times
+over (the full-size tests reach them that way); here the switch AMSIM_WIDE=1 sends every
+eligible fast-mode launch through them, so ragged tiles, padding edges, strides, 1x1
+GEMM routing, batched matmuls, the fused epilogue and both table kinds are compared with
+the CPU oracle at sizes it finishes in a moment.  Bar: rel-L2 <= 1e-5 against the
+reference-order result; where one thread owns an output's whole reduction (plain grid)
+and no operand is zero the result must be bit-identical.
+"""
+import zlib
+
+import numpy as np
+import pytest
+
+from conftest import lut_path, rel_l2, set_switch
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def ops():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from approxtrain_b200 import ops as o
+    return o
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def close(got, want, what):
+    r = rel_l2(got, want)
+    print(f"{what}: rel-L2 {r:.3e} max-abs {np.abs(np.asarray(got) - np.asarray(want)).max():.3e}")
+    assert np.asarray(got).shape == np.asarray(want).shape
+    assert r <= REL_L2_TOL, f"{what}: rel-L2 {r}"
+
+
+def launches():
+    from approxtrain_b200 import _lib
+    return _lib.lib.amsim_debug_launch_count()
+
+
+# (n, h, w, c, kh, kw, k, stride, padding): channel counts are multiples of 4 (128-bit gathers) and
+# more than 32 output columns, which is what the wide kernels take
+WIDE_CONV = [
+    (2, 9, 8, 8, 3, 3, 48, 1, "SAME"),       # one ragged 256-row tile, 144 of them valid
+    (3, 17, 19, 12, 3, 2, 70, 1, "VALID"),   # several row tiles, ragged columns, asymmetric filter
+    (2, 13, 13, 16, 3, 3, 64, 2, "SAME"),    # stride 2: input gradient runs one sub-convolution per phase
+    (1, 20, 20, 32, 1, 1, 96, 1, "VALID"),   # 1x1: plain GEMM routing
+    (2, 11, 11, 64, 1, 1, 256, 2, "VALID"),  # strided 1x1 projection
+    (4, 10, 10, 32, 3, 3, 40, 1, "SAME"),    # filter gradient: 288 rows = one 9-rows-per-lane tile
+    (2, 6, 6, 8, 5, 5, 36, 1, "SAME"),       # 5x5
+]
+
+
+@pytest.mark.parametrize("balanced", ["0", "1"])
+@pytest.mark.parametrize("lname", ["MBM_7", "MIT_7", "MBM_5"])
+@pytest.mark.parametrize("case", WIDE_CONV)
+def test_wide_conv_all_directions(ops, oracle, luts, monkeypatch, case, lname, balanced):
+    n, h, w, c, kh, kw, k, s, pad = case
+    set_switch(monkeypatch, "AMSIM_WIDE", "1")
+    set_switch(monkeypatch, "AMSIM_WIDE_BALANCED", balanced)
+    lut, m = luts[lname]
+    rng = np.random.default_rng(zlib.crc32(repr((case, lname)).encode()))
+    x = rng.standard_normal((n, h, w, c)).astype(np.float32)
+    x[x < -0.8] = 0.0                      # zeros as after a ReLU
+    wt = rng.standard_normal((kh, kw, c, k)).astype(np.float32)
+    g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+    dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+    dy[dy < -1.0] = 0.0
+    kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=lut_path(lname))
+    close(ops.convam(dev(x), dev(wt), **kw_).cpu().numpy(), oracle.conv2d_fwd(g, x, wt, lut, m), "wide fwd")
+    close(ops.convam_input_grad(x.shape, dev(wt), dev(dy), **kw_).cpu().numpy(), oracle.conv2d_bwd_input(g, wt, dy, lut, m),
+          "wide input-grad")
+    close(ops.convam_filter_grad(wt.shape, dev(x), dev(dy), **kw_).cpu().numpy(), oracle.conv2d_bwd_filter(g, x, dy, lut, m),
+          "wide filter-grad")
+
+
+def test_wide_plain_grid_keeps_the_reference_chain(ops, oracle, luts, monkeypatch):
+    """Plain grid: one thread owns an output's whole reduction in ascending order, so without zero
+    operands the fast result equals the oracle bit for bit (forward and input gradient)."""
+    set_switch(monkeypatch, "AMSIM_WIDE", "1")
+    set_switch(monkeypatch, "AMSIM_WIDE_BALANCED", "0")
+    for lname in ("MBM_7", "MIT_7"):
+        lut, m = luts[lname]
+        rng = np.random.default_rng(5)
+        x = rng.standard_normal((2, 14, 14, 16)).astype(np.float32)
+        wt = rng.standard_normal((3, 3, 16, 48)).astype(np.float32)
+        g = oracle.geometry(2, 14, 14, 16, 3, 3, 48, 1, 1, "VALID")
+        dy = rng.standard_normal((2, g.out_h, g.out_w, 48)).astype(np.float32)
+        kw_ = dict(strides=[1, 1, 1, 1], padding="VALID", mant_mul_lut=lut_path(lname))
+        y = ops.convam(dev(x), dev(wt), **kw_).cpu().numpy()
+        assert np.array_equal(y.view(np.uint32), oracle.conv2d_fwd(g, x, wt, lut, m).view(np.uint32)), lname
+
+
+def test_wide_kernels_are_the_ones_that_ran(ops, oracle, luts, monkeypatch):
+    """AMSIM_WIDE=0 and =1 give the same numbers within the bar through different kernels: the
+    filter gradient's split count differs (2 vs 3 resident CTAs per multiprocessor), so the two
+    results are close but not identical; with the switch off and on again the result repeats."""
+    lut, m = luts["MBM_7"]
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((16, 40, 40, 32)).astype(np.float32)   # 25 600 pixels: room for 148 and for 296 splits
+    dy = rng.standard_normal((16, 40, 40, 64)).astype(np.float32)
+    kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=lut_path("MBM_7"))
+    g = oracle.geometry(16, 40, 40, 32, 3, 3, 64, 1, 1, "SAME")
+    want = oracle.conv2d_bwd_filter(g, x, dy, lut, m)
+    out = {}
+    for sw in ("0", "1", "0", "1"):
+        set_switch(monkeypatch, "AMSIM_WIDE", sw)
+        got = ops.convam_filter_grad((3, 3, 32, 64), dev(x), dev(dy), **kw_).cpu().numpy()
+        close(got, want, f"filter-grad AMSIM_WIDE={sw}")
+        if sw in out:
+            assert np.array_equal(out[sw], got), "same switch, same kernel, same bits"
+        out[sw] = got
+    assert not np.array_equal(out["0"], out["1"]), "both settings ran the same kernel"
+
+
+@pytest.mark.parametrize("balanced", ["0", "1"])
+def test_wide_dense_and_matmul(ops, oracle, luts, monkeypatch, balanced):
+    set_switch(monkeypatch, "AMSIM_WIDE", "1")
+    set_switch(monkeypatch, "AMSIM_WIDE_BALANCED", balanced)
+    lut, m = luts["MBM_7"]
+    lp = lut_path("MBM_7")
+    rng = np.random.default_rng(12)
+    for b, kin, u in ((300, 64, 72), (513, 128, 260), (40, 512, 1000)):
+        x = rng.random((b, kin)).astype(np.float32)
+        x[x < 0.3] = 0
+        w = (rng.standard_normal((kin, u)) * 0.1).astype(np.float32)
+        gy = (rng.standard_normal((b, u)) * 0.01).astype(np.float32)
+        close(ops.denseam(dev(x), dev(w), lp).cpu().numpy(), oracle.dense_fwd(x, w, lut, m), f"wide dense fwd {b}x{kin}x{u}")
+        dx, dw = ops.denseam_grad(dev(gy), dev(x), dev(w), lp)
+        close(dx.cpu().numpy(), oracle.dense_bwd_input(w, gy, lut, m), "wide dense input-grad")
+        close(dw.cpu().numpy(), oracle.dense_bwd_weight(x, gy, lut, m), "wide dense weight-grad")
+    # batched products of an attention layer, K read transposed, with the score scale in the epilogue
+    q = rng.standard_normal((6, 130, 64)).astype(np.float32)
+    kk = rng.standard_normal((6, 70, 64)).astype(np.float32)
+    alpha = np.float32(0.125)
+    want = (oracle.matmul(q, np.ascontiguousarray(kk.transpose(0, 2, 1)), lut, m) * alpha).astype(np.float32)
+    close(ops.matmulam(dev(q), dev(kk), transpose_b=True, mant_mul_lut=lp, alpha=float(alpha)).cpu().numpy(), want,
+          "wide matmul, transposed b, alpha")
+    a = rng.standard_normal((3, 260, 36)).astype(np.float32)
+    b2 = rng.standard_normal((36, 44)).astype(np.float32)      # rank-2 operand broadcasts over the batch
+    close(ops.matmulam(dev(a), dev(b2), mant_mul_lut=lp).cpu().numpy(), oracle.matmul(a, np.broadcast_to(b2, (3, 36, 44)).copy(), lut, m),
+          "wide matmul, broadcast b")
+
+
+def test_wide_fused_epilogue_is_bit_identical_to_the_unfused_sequence(ops, luts, monkeypatch):
+    set_switch(monkeypatch, "AMSIM_WIDE", "1")
+    rng = np.random.default_rng(4)
+    x = dev(rng.standard_normal((2, 12, 12, 16)).astype(np.float32))
+    wt = dev(rng.standard_normal((3, 3, 16, 48)).astype(np.float32))
+    bias = dev(rng.standard_normal(48).astype(np.float32))
+    scale = dev((rng.random(48) + 0.5).astype(np.float32))
+    kw_ = dict(strides=[1, 1, 1, 1], padding="SAME", mant_mul_lut=lut_path("MBM_7"))
+    y = ops.convam(x, wt, **kw_)
+    fused = ops.convam_bias_act(x, wt, bias, activation="relu", scale=scale, **kw_)
+    assert torch.equal(fused, torch.relu(y * scale + bias))
