@@ -27,7 +27,7 @@ EXPORTS = [
     "amsim_dense_fwd",
     "amsim_dense_bwd_weight_workspace", "amsim_dense_bwd_weight", "amsim_dense_bwd_input", "amsim_matmul",
     "amsim_matmul_ex",
-    "amsim_debug_fastdiv", "amsim_debug_launch_count", "amsim_debug_reload_env",
+    "amsim_debug_fastdiv", "amsim_debug_launch_count", "amsim_debug_reload_env", "amsim_debug_bounds_report",
 ]
 
 
@@ -74,6 +74,7 @@ def _load() -> C.CDLL:
     L.amsim_debug_fastdiv.restype = C.c_uint32
     L.amsim_debug_launch_count.argtypes = []
     L.amsim_debug_launch_count.restype = C.c_ulonglong
+    L.amsim_debug_bounds_report.argtypes = [C.POINTER(C.c_ulonglong)]
     L.amsim_debug_reload_env.argtypes = []
     L.amsim_debug_reload_env.restype = None
     return L

@@ -66,8 +66,9 @@ struct Switches {
   int thin_fast = -1;       // AMSIM_THIN_FAST=0/1       fast filter gradient of tiny outputs
   int exact_only = 0;       // AMSIM_EXACT_ONLY=1        deterministic kernels never use the fast arithmetic
   int no_additive = 0;      // AMSIM_NO_ADDITIVE=1       additive tables are looked up like any other (at lut_open)
-  int wide = -1;            // AMSIM_WIDE=0/1            16 x 8 register-tile kernels: never / whenever eligible
-  int wide_balanced = -1;   // AMSIM_WIDE_BALANCED=0/1   their balanced launch
+  int wide = -1;            // AMSIM_WIDE=0/1            wide-tile filter gradient: never / whenever eligible
+  int bounds_shrink = 0;    // AMSIM_BOUNDS_SHRINK=n     bounds-checking build only: the output's recorded extent is n bytes
+                            //                           short, so its last stores are caught (self-test of the checker)
 };
 Switches g_sw;
 std::once_flag g_sw_once;
@@ -91,7 +92,7 @@ void load_switches() {
   flag("AMSIM_EXACT_ONLY", w.exact_only);
   flag("AMSIM_NO_ADDITIVE", w.no_additive);
   tri("AMSIM_WIDE", w.wide);
-  tri("AMSIM_WIDE_BALANCED", w.wide_balanced);
+  tri("AMSIM_BOUNDS_SHRINK", w.bounds_shrink);
   g_sw = w;
 }
 
@@ -114,6 +115,42 @@ int sm_count(int device) {
   }
   known[device] = sms;
   return sms;
+}
+
+#ifdef AMSIM_BOUNDS_CHECK
+// Device word that records the first bad access of a bounds-checking build (one per device).
+unsigned long long* bounds_word(int device) {
+  static std::mutex mu;
+  static std::map<int, unsigned long long*> words;
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = words.find(device);
+  if (it != words.end()) return it->second;
+  unsigned long long* w = nullptr;
+  if (cudaMalloc(&w, sizeof(*w)) != cudaSuccess || cudaMemset(w, 0, sizeof(*w)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    w = nullptr;
+  }
+  words[device] = w;
+  return w;
+}
+#endif
+
+// Bounds-checking build: the extents the kernels' accesses are compared with.
+void fill_bounds(amsim::Params& p, int device, const void* ws, size_t ws_bytes) {
+#ifdef AMSIM_BOUNDS_CHECK
+  const void* base[3] = {p.V, p.U, p.O};
+  const long long elems[3] = {p.v_elems, p.u_elems, p.o_elems};
+  for (int i = 0; i < 3; ++i) {
+    p.bnd.lo[i] = static_cast<const char*>(base[i]);
+    p.bnd.hi[i] = p.bnd.lo[i] + elems[i] * 4;
+  }
+  if (sw().bounds_shrink > 0) p.bnd.hi[amsim::BUF_O] -= sw().bounds_shrink;
+  p.bnd.lo[amsim::BUF_WS] = static_cast<const char*>(ws);
+  p.bnd.hi[amsim::BUF_WS] = static_cast<const char*>(ws) + ws_bytes;
+  p.bnd.report = bounds_word(device);
+#else
+  (void)p; (void)device; (void)ws; (void)ws_bytes;
+#endif
 }
 
 int current_device() {
@@ -360,75 +397,63 @@ int scratch_alloc(cudaStream_t st, int device, size_t bytes, float** out) {
   return AMSIM_OK;
 }
 
-// ---- 16 x 8 register-tile kernels (amsim_wide.cuh) ------------------------------------------------
-// Rate of the wide kernels relative to the 16 x 4 kernels (time per padded product), used to weigh
-// their larger tile padding against their cheaper operand fetch.
-constexpr double kWideRate = 0.93;
+// Scratch of a balanced launch.  Outside a graph capture it is a stream-ordered allocation (safe for
+// launches on several streams at once).  While the stream is being captured nothing may be
+// allocated, so a capture uses one persistent buffer per device: every eager balanced launch makes
+// sure that buffer is at least as large as its own scratch (growing it is the one place where this
+// library calls cudaMalloc after a LUT is open; it happens a handful of times, on the first eager
+// steps), so a capture that follows a few warm-up steps of the same shapes finds room; a capture that
+// does not takes the plain / cluster launch instead.  The nodes of one captured stream run in order,
+// so they can share the buffer; graphs that are replayed concurrently on several streams must not
+// both contain balanced launches.
+struct BalancedScratch {
+  float* ws = nullptr;
+  bool pooled = false;
+};
 
-template <int LM>
-int launch_wide_gather(cudaStream_t st, Params& p, int batch, int device, bool* taken) {
-  *taken = false;
-  if (sw().wide == 0 || p.Q <= 32) return AMSIM_OK;
-  const int nkb = (p.K + BK - 1) / BK;
-  const int ptiles = (p.P + WBP - 1) / WBP, qtiles = (p.Q + BQ - 1) / BQ;
-  const long long ctas = (long long)ptiles * qtiles * batch;
-  if (sw().wide < 0) {
-    // worth it when the problem fills the device a few times over and the 256-row tiles do not
-    // pad away what the cheaper operand fetch gains
-    const long long rows_w = (long long)ptiles * WBP, rows_n = (long long)((p.P + 127) / 128) * 128;
-    if ((double)rows_w * kWideRate >= (double)rows_n) return AMSIM_OK;
-    if (ctas * nkb < 8ll * 2 * sm_count(device)) return AMSIM_OK;
-  }
-  p.tile_bytes = wide_tile_bytes(0);
-  const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
-  int rc = ensure_smem(wide_gather<LM, GM_BALANCED>, smem, device);
-  if (rc) return rc;
-  rc = ensure_smem(wide_gather<LM, GM_PLAIN>, smem, device);
-  if (rc) return rc;
-  int slots = 0;
-  rc = resident_slots(wide_gather<LM, GM_BALANCED>, smem, device, &slots);
-  if (rc) return rc;
-  const long long iters = ctas * nkb;
-  const long long waves = slots > 0 ? (ctas + slots - 1) / slots : 1;
-  const double fill = slots > 0 ? (double)ctas / (double)(waves * slots) : 1.0;
-  long long grid = slots;
-  if (iters / (grid > 0 ? grid : 1) < 2) grid = iters / 2;
-  int balanced = fill < 0.93 && grid >= 2 && nkb >= 2;
-  if (sw().wide_balanced >= 0) balanced = sw().wide_balanced != 0 && grid >= 1;
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  CUDA_TRY(cudaStreamIsCapturing(st, &cap));
-  *taken = true;
-  if (balanced && cap == cudaStreamCaptureStatusNone && slots > 0) {
-    p.sk_iters = iters;
-    p.sk_ptiles = ptiles;
-    p.sk_qtiles = qtiles;
-    p.sk_grid = (int)grid;
-    const size_t slot_bytes = (size_t)grid * 2 * W_ACC * sizeof(float);
-    const size_t bytes = slot_bytes + (size_t)ctas * sizeof(int);
-    rc = scratch_alloc(st, device, bytes, &p.ws);
-    if (rc == AMSIM_OK) {
-      p.sk_count = reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) + slot_bytes);
-      cudaError_t e1 = cudaMemsetAsync(p.sk_count, 0, (size_t)ctas * sizeof(int), st);
-      if (e1 == cudaSuccess) {
-        AMSIM_COUNT_LAUNCH();
-        wide_gather<LM, GM_BALANCED><<<dim3((unsigned)grid), WNT, smem, st>>>(p);
-        e1 = cudaGetLastError();
-      }
-      cudaError_t e2 = cudaFreeAsync(p.ws, st);
-      p.ws = nullptr;
-      p.sk_count = nullptr;
-      CUDA_TRY(e1);
-      CUDA_TRY(e2);
-      return AMSIM_OK;
+int balanced_scratch_acquire(cudaStream_t st, int device, size_t bytes, bool capturing, BalancedScratch* out) {
+  static std::mutex mu;
+  static std::map<int, std::pair<void*, size_t>> persistent;
+  out->ws = nullptr;
+  out->pooled = false;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto& slot = persistent[device];
+    if (capturing) {
+      if (slot.first && slot.second >= bytes) out->ws = static_cast<float*>(slot.first);
+      return AMSIM_OK;  // ws stays null when there is no room: the caller launches without scratch
     }
-    (void)cudaGetLastError();  // no scratch to be had: the plain grid needs none
-    p.ws = nullptr;
+    if (slot.second < bytes) {
+      void* fresh = nullptr;
+      if (cudaMalloc(&fresh, bytes) == cudaSuccess) {
+        // the old buffer may still be referenced by instantiated graphs: it is kept, not freed
+        slot.first = fresh;
+        slot.second = bytes;
+      } else {
+        (void)cudaGetLastError();
+      }
+    }
   }
-  AMSIM_COUNT_LAUNCH();
-  wide_gather<LM, GM_PLAIN><<<dim3(ptiles, qtiles, batch), WNT, smem, st>>>(p);
-  CUDA_TRY(cudaGetLastError());
+  if (scratch_alloc(st, device, bytes, &out->ws) != AMSIM_OK) {
+    (void)cudaGetLastError();
+    out->ws = nullptr;
+    return AMSIM_OK;
+  }
+  out->pooled = true;
   return AMSIM_OK;
 }
+
+cudaError_t balanced_scratch_release(cudaStream_t st, const BalancedScratch& b) {
+  return b.pooled ? cudaFreeAsync(b.ws, st) : cudaSuccess;
+}
+
+// ---- 16 x 8 / 16 x 9 register-tile filter gradient (amsim_wide.cuh) ---------------------------------
+// Measured rate of wide_fgrad relative to fgrad_gemm (time per padded product) on the 3x3
+// microbenchmark shapes, used to weigh tile padding against operand-fetch cost.  With a table in
+// shared memory it is about 3 % slower per padded product (8 instead of 12 warps per
+// multiprocessor hide less lookup latency) and only pays where its 288-row tiles remove padding
+// (576 rows: 1.40 -> 1.30 ms); with an additive table (no lookups, issue bound) it is 20-28 % faster.
+constexpr double kWideRateTable = 1.03, kWideRateAdditive = 0.80;
 
 template <bool EXACT, bool VEC, int LM>
 int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
@@ -439,14 +464,6 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
   p.ksplit = 1;
   p.tile_bytes = L::TILE_BYTES;
   const size_t smem_plain = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : L::bytes(p.tile_bytes, p.lut_bytes, p.lut_align);
-
-  // Fast mode, large launches with 128-bit gathers: the 16 x 8 register-tile kernel.
-  if constexpr (!EXACT && VEC && (LM == LM_SMEM || LM == LM_ADD)) {
-    bool taken = false;
-    int rc = launch_wide_gather<LM>(st, p, batch, device, &taken);
-    if (rc || taken) return rc;
-    p.tile_bytes = L::TILE_BYTES;
-  }
 
   // Fast mode, narrow outputs (at most 32 columns: first-layer input gradients, small heads, LeNet-5's
   // convolutions): 2 or 4 warps share each 16-column group and split the reduction steps.
@@ -472,8 +489,8 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
 
   // Fast mode, balanced launch: the plain grid would leave the last wave of resident CTA slots
   // partly empty (or never fill them), so the (tile, reduction block) pairs are dealt out in
-  // equal runs to exactly as many CTAs as the device holds.  Not taken while the stream is
-  // being captured into a graph (the scratch comes from the stream-ordered allocator).
+  // equal runs to exactly as many CTAs as the device holds.  While the stream is being
+  // captured into a graph the scratch is a persistent buffer (see balanced_scratch_acquire).
   // (not for tables in global memory: those launches are bound by L2 gathers, and lock-step CTAs
   // measured 50 % slower there)
   if constexpr (!EXACT && !lm_global(LM)) {
@@ -495,31 +512,34 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
     if (sw().balanced >= 0) mode = sw().balanced != 0 && grid >= 1;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     CUDA_TRY(cudaStreamIsCapturing(st, &cap));
-    if (mode && cap == cudaStreamCaptureStatusNone && slots > 0) {
+    if (mode && slots > 0) {
       p.sk_iters = iters;
       p.sk_ptiles = ptiles;
       p.sk_qtiles = qtiles;
       p.sk_grid = (int)grid;
       const size_t slot_bytes = (size_t)grid * 2 * TR * TC * L::NT * sizeof(float);
       const size_t bytes = slot_bytes + (size_t)ctas * sizeof(int);
-      rc = scratch_alloc(st, device, bytes, &p.ws);
-      if (rc == AMSIM_OK) {
-      p.sk_count = reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) + slot_bytes);
-      cudaError_t e1 = cudaMemsetAsync(p.sk_count, 0, (size_t)ctas * sizeof(int), st);
-      if (e1 == cudaSuccess) {
-        AMSIM_COUNT_LAUNCH();
-        gather_gemm<1, EXACT, VEC, GM_BALANCED, LM><<<dim3((unsigned)grid), L::NT, smem_plain, st>>>(p);
-        e1 = cudaGetLastError();
+      BalancedScratch sc;
+      rc = balanced_scratch_acquire(st, device, bytes, cap != cudaStreamCaptureStatusNone, &sc);
+      if (rc) return rc;
+      if (sc.ws) {
+        p.ws = sc.ws;
+        p.sk_count = reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) + slot_bytes);
+        fill_bounds(p, device, p.ws, bytes);
+        cudaError_t e1 = cudaMemsetAsync(p.sk_count, 0, (size_t)ctas * sizeof(int), st);
+        if (e1 == cudaSuccess) {
+          AMSIM_COUNT_LAUNCH();
+          gather_gemm<1, EXACT, VEC, GM_BALANCED, LM><<<dim3((unsigned)grid), L::NT, smem_plain, st>>>(p);
+          e1 = cudaGetLastError();
+        }
+        cudaError_t e2 = balanced_scratch_release(st, sc);
+        p.ws = nullptr;
+        p.sk_count = nullptr;
+        CUDA_TRY(e1);
+        CUDA_TRY(e2);
+        return AMSIM_OK;
       }
-      cudaError_t e2 = cudaFreeAsync(p.ws, st);
-      p.ws = nullptr;
-      p.sk_count = nullptr;
-      CUDA_TRY(e1);
-      CUDA_TRY(e2);
-      return AMSIM_OK;
-      }
-      // no scratch to be had (pool exhausted, allocator unsupported): the plain grid needs none
-      (void)cudaGetLastError();
+      // no scratch to be had (pool exhausted, or a capture without a warm-up): the plain grid needs none
       p.ws = nullptr;
     }
   }
@@ -565,6 +585,7 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
 }
 int launch_gather(cudaStream_t st, Params& p, int batch, bool exact, int device) {
   if (p.P <= 0 || p.Q <= 0 || batch <= 0) return AMSIM_OK;  // nothing to compute
+  fill_bounds(p, device, nullptr, 0);
   if ((long long)p.P >= (1ll << 31) - 256) return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 output rows");
   const bool vec = !p.v_trans && (p.g.SC % 4 == 0) && aligned16(p.V) && (p.v_bs % 4 == 0);
   // U by 128-bit loads along its contiguous index when four elements are always one aligned
@@ -599,19 +620,20 @@ struct FgradPlan {
   size_t ws_bytes;
 };
 
-// Rows per lane a fast-mode filter gradient of P x Q outputs would take if its operands allow the
-// wide kernel (128-bit gathers, table in shared memory or additive): the tile height with the least
-// padded work, weighted by the kernels' rates.  0 = the 128-row kernel.
-int pick_fgrad_rows(int P, int Q, int K, int sms) {
+// Rows per lane a fast-mode filter gradient of P x Q outputs takes if its operands allow the wide
+// kernel (128-bit gathers; `additive`: the table is additive, else it sits in shared memory): the
+// tile height with the least padded work, weighted by the kernels' measured rates.  0 = the
+// 128-row kernel.
+int pick_fgrad_rows(int P, int Q, int K, int sms, bool additive) {
   if (sw().wide == 0) return 0;
-  auto padded = [&](int bp) { return (double)((P + bp - 1) / bp) * bp; };
+  auto padded = [&](int bp) { return (double)(((long long)P + bp - 1) / bp) * bp; };
   int best = 8;
   double cost = padded(256);
   if (padded(288) < cost) { best = 9; cost = padded(288); }
   if (sw().wide > 0) return best;
-  if (cost * kWideRate >= padded(128)) return 0;
-  const long long tiles = (long long)((P + 32 * best - 1) / (32 * best)) * ((Q + BQ - 1) / BQ);
-  if (tiles * ((K + BK - 1) / BK) < 8ll * 2 * sms) return 0;  // too small to fill the device a few times over
+  if (cost * (additive ? kWideRateAdditive : kWideRateTable) >= padded(128)) return 0;
+  const long long tiles = (((long long)P + 32 * best - 1) / (32 * best)) * (((long long)Q + BQ - 1) / BQ);
+  if (tiles * (((long long)K + BK - 1) / BK) < 8ll * 2 * sms) return 0;  // too small to fill the device a few times over
   return best;
 }
 
@@ -623,7 +645,7 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact, int np, int sms) {
   f.np = exact ? 0 : np;
   const int bp = f.np ? 32 * f.np : 128;
   const int slots = sms * (f.np ? 2 : AMSIM_CTAS1);  // resident CTAs on the whole GPU (launch bounds of the kernels)
-  const long long tiles = (long long)((P + bp - 1) / bp) * ((Q + BQ - 1) / BQ);
+  const long long tiles = (((long long)P + bp - 1) / bp) * (((long long)Q + BQ - 1) / BQ);
   const long long chains = (long long)P * Q;
   f.thin = 0;
   f.tq = 1;
@@ -641,24 +663,24 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact, int np, int sms) {
     f.thin = !f.np && (double)chains < 0.2 * (double)(tiles * bp * BQ);
     if (sw().thin_fast >= 0 && !f.np) f.thin = sw().thin_fast != 0;
     if (f.thin) {
-      const int nw = (Q + f.tq - 1) / f.tq > 4 ? 16 : 4;
-      const long long ctas = (long long)((P + 31) / 32) * ((Q + nw * f.tq - 1) / (nw * f.tq));
+      const int nw = ((long long)Q + f.tq - 1) / f.tq > 4 ? 16 : 4;
+      const long long ctas = (((long long)P + 31) / 32) * (((long long)Q + nw * f.tq - 1) / (nw * f.tq));
       splits = (int)(4 * sms / ctas);
-      const int max_splits = (K + 2 * BK - 1) / (2 * BK);  // at least 2 stages per split
+      const int max_splits = (int)(((long long)K + 2 * BK - 1) / (2 * BK));  // at least 2 stages per split
       if (splits > max_splits) splits = max_splits;
     } else {
       // one balanced wave: as many splits as fit in the resident slots
       splits = (int)(slots / tiles);
-      const int max_splits = (K + 4 * BK - 1) / (4 * BK);  // at least 4 stages per split
+      const int max_splits = (int)(((long long)K + 4 * BK - 1) / (4 * BK));  // at least 4 stages per split
       if (splits > max_splits) splits = max_splits;
     }
     if (splits < 1) splits = 1;
   }
-  int chunk = (K + splits - 1) / splits;
+  long long chunk = ((long long)K + splits - 1) / splits;
   chunk = (chunk + BK - 1) / BK * BK;
   if (chunk < BK) chunk = BK;
-  f.k_chunk = chunk;
-  f.splits = K > 0 ? (K + chunk - 1) / chunk : 1;
+  f.k_chunk = (int)chunk;
+  f.splits = K > 0 ? (int)(((long long)K + chunk - 1) / chunk) : 1;
   f.ws_bytes = f.splits > 1 ? (size_t)f.splits * P * Q * sizeof(float) : 0;
   return f;
 }
@@ -668,8 +690,10 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact, int np, int sms) {
 size_t fgrad_workspace(int P, int Q, int K, bool exact, int sms) {
   size_t need = plan_fgrad(P, Q, K, exact, 0, sms).ws_bytes;
   if (!exact) {
-    const int np = pick_fgrad_rows(P, Q, K, sms);
-    if (np) need = std::max(need, plan_fgrad(P, Q, K, false, np, sms).ws_bytes);
+    for (int additive = 0; additive < 2; ++additive) {
+      const int np = pick_fgrad_rows(P, Q, K, sms, additive != 0);
+      if (np) need = std::max(need, plan_fgrad(P, Q, K, false, np, sms).ws_bytes);
+    }
   }
   return need;
 }
@@ -763,7 +787,7 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
   FgradPlan f = plan_fgrad(p.P, p.Q, p.K, exact, 0, sms);
   if (!exact && !f.thin && vec && (p.lut_mode == LM_SMEM || p.lut_mode == LM_ADD)) {
-    const int np = pick_fgrad_rows(p.P, p.Q, p.K, sms);
+    const int np = pick_fgrad_rows(p.P, p.Q, p.K, sms, p.lut_mode == LM_ADD);
     if (np) f = plan_fgrad(p.P, p.Q, p.K, false, np, sms);
   }
   if (f.ws_bytes > 0) {
@@ -774,6 +798,7 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   p.splits = f.splits;
   p.k_chunk = f.k_chunk;
   p.ws = static_cast<float*>(ws);
+  fill_bounds(p, device, ws, f.ws_bytes);
   if (f.np) {
     p.u_vec = aligned16(p.U) && p.u_sq == 1 && p.u_sk % 4 == 0 && p.Q % 4 == 0 && !sw().no_uvec;
     if (p.lut_mode == LM_ADD)
@@ -837,14 +862,23 @@ int launch_naive_i32(cudaStream_t st, Params& p, const amsim_lut* lut, bool fgra
   return AMSIM_OK;
 }
 
+// a * b * c < lim for non-negative ints, without overflowing
+inline bool prod3_below(long long a, long long b, long long c, long long lim) {
+  if (a == 0 || b == 0 || c == 0) return lim > 0;
+  if (a >= lim || b >= lim || c >= lim) return false;
+  const long long ab = a * b;  // < lim^2 <= 2^62
+  if (ab >= lim) return false;
+  return ab * c < lim;         // < lim^2
+}
+
 int check_conv_dims(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h, int out_w,
                     int stride_h, int stride_w, int pad_top, int pad_left) {
   if (batch < 0 || in_h <= 0 || in_w <= 0 || in_c <= 0 || f_h <= 0 || f_w <= 0 || out_c <= 0 || out_h < 0 ||
       out_w < 0 || stride_h <= 0 || stride_w <= 0 || pad_top < 0 || pad_left < 0)
     return fail(AMSIM_ERR_INVALID, "convolution dimensions must be positive (strides > 0, pads >= 0)");
-  if ((long long)f_h * f_w * (long long)(in_c > out_c ? in_c : out_c) >= (1ll << 30))
+  if (!prod3_below(f_h, f_w, in_c > out_c ? in_c : out_c, 1ll << 30))
     return fail(AMSIM_ERR_UNSUPPORTED, "reduction length exceeds 2^30");
-  if ((long long)batch * in_h * in_w >= (1ll << 31) - 256 || (long long)batch * out_h * out_w >= (1ll << 31) - 256)
+  if (!prod3_below(batch, in_h, in_w, (1ll << 31) - 256) || !prod3_below(batch, out_h, out_w, (1ll << 31) - 256))
     return fail(AMSIM_ERR_UNSUPPORTED, "more than 2^31 pixels");
   return AMSIM_OK;
 }
@@ -858,6 +892,22 @@ const char* amsim_last_error(void) { return g_err; }
 const char* amsim_version(void) { return "amsim 0.1 (sm_100a)"; }
 
 unsigned long long amsim_debug_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int amsim_debug_bounds_report(unsigned long long* word) {
+  if (word) *word = 0;
+#ifdef AMSIM_BOUNDS_CHECK
+  unsigned long long* w = bounds_word(current_device());
+  if (!w) return fail(AMSIM_ERR_CUDA, "no bounds-report word on this device");
+  CUDA_TRY(cudaDeviceSynchronize());
+  unsigned long long v = 0;
+  CUDA_TRY(cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost));
+  CUDA_TRY(cudaMemset(w, 0, sizeof(v)));
+  if (word) *word = v;
+  return AMSIM_OK;
+#else
+  return fail(AMSIM_ERR_UNSUPPORTED, "this library was built without -DAMSIM_BOUNDS_CHECK");
+#endif
+}
 
 void amsim_debug_reload_env(void) {
   sw();  // make sure the one-time load has happened, then replace its result
@@ -1023,6 +1073,8 @@ static int conv2d_fwd_impl(void* stream, const amsim_lut* lut, const float* x, c
   if (!x || !w || !y) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   Params p{};
   p.V = x; p.U = w; p.O = y;
+  p.v_elems = (long long)batch * in_h * in_w * in_c; p.u_elems = (long long)f_h * f_w * in_c * out_c;
+  p.o_elems = (long long)batch * out_h * out_w * out_c;
   p.P = batch * out_h * out_w; p.Q = out_c; p.K = f_h * f_w * in_c;
   Gather& g = p.g;
   g.PH = out_h; g.PW = out_w; g.ps_h = stride_h; g.ps_w = stride_w; g.off_t = pad_top; g.off_l = pad_left;
@@ -1081,6 +1133,8 @@ int amsim_conv2d_bwd_input(void* stream, const amsim_lut* lut, const float* w, c
   const int bpt = f_h - 1 - pad_top, bpl = f_w - 1 - pad_left;                        // convam.cc:1083-1084
   Params p{};
   p.V = dy; p.U = w; p.O = dx;
+  p.v_elems = (long long)batch * out_h * out_w * out_c; p.u_elems = (long long)f_h * f_w * in_c * out_c;
+  p.o_elems = (long long)batch * in_h * in_w * in_c;
   p.Q = in_c;
   p.u_tap = (long long)in_c * out_c; p.u_sk = 1; p.u_sq = out_c;  // w[tap][c][ko]: element (ko; c)
   p.o_sp = in_c; p.o_sq = 1;
@@ -1150,6 +1204,7 @@ static void setup_wgrad(Params& p, const amsim_lut* lut, const float* x, const f
   p.V = swap ? g_ : x;
   p.U = swap ? x : g_;
   p.O = dw;
+  p.v_elems = rows * (swap ? units : in_w); p.u_elems = rows * (swap ? in_w : units); p.o_elems = (long long)in_w * units;
   p.P = swap ? units : in_w;
   p.Q = swap ? in_w : units;
   p.K = (int)rows;
@@ -1167,8 +1222,9 @@ static void setup_wgrad(Params& p, const amsim_lut* lut, const float* x, const f
 static size_t conv_fgrad_workspace(int batch, int in_h, int in_w, int in_c, int f_h, int f_w, int out_c, int out_h,
                                    int out_w, bool det, int sms) {
   if (batch <= 0 || in_c <= 0 || f_h <= 0 || f_w <= 0 || out_c <= 0 || out_h <= 0 || out_w <= 0) return 0;
+  if (!prod3_below(f_h, f_w, in_c > out_c ? in_c : out_c, 1ll << 30) || !prod3_below(batch, out_h, out_w, (1ll << 31) - 256))
+    return 0;
   const long long rows = (long long)f_h * f_w * in_c, npix = (long long)batch * out_h * out_w;
-  if (rows >= (1ll << 30) || (long long)f_h * f_w * out_c >= (1ll << 30) || npix >= (1ll << 31) - 256) return 0;
   size_t need = fgrad_workspace((int)rows, out_c, (int)npix, det, sms);
   // a 1x1 stride-1 convolution may run with the operand roles swapped (wgrad_swap): cover both plans
   if (f_h == 1 && f_w == 1 && out_h == in_h && out_w == in_w && wgrad_swap(in_c, out_c))
@@ -1208,6 +1264,7 @@ int amsim_conv2d_bwd_filter(void* stream, const amsim_lut* lut, const float* x, 
   }
   Params p{};
   p.V = x; p.U = dy; p.O = dw;
+  p.v_elems = (long long)batch * in_h * in_w * in_c; p.u_elems = npix * out_c; p.o_elems = (long long)f_h * f_w * in_c * out_c;
   p.P = f_h * f_w * in_c; p.Q = out_c; p.K = (int)npix;
   Gather& g = p.g;
   g.PH = out_h; g.PW = out_w; g.ps_h = stride_h; g.ps_w = stride_w; g.off_t = pad_top; g.off_l = pad_left;
@@ -1275,6 +1332,8 @@ static void dense_gather(Gather& g, int width) {
 
 static int check_dense(int batch, int units, int input_width) {
   if (batch < 0 || units <= 0 || input_width <= 0) return fail(AMSIM_ERR_INVALID, "dense dimensions must be positive");
+  if (units >= (1 << 30) || input_width >= (1 << 30) || (long long)batch >= (1ll << 31) - 256)
+    return fail(AMSIM_ERR_UNSUPPORTED, "dense dimensions exceed 2^30 columns or 2^31 rows");
   return AMSIM_OK;
 }
 
@@ -1289,6 +1348,7 @@ static int dense_fwd_impl(void* stream, const amsim_lut* lut, const float* x, co
   if (!x || !w || !y) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   Params p{};
   p.V = x; p.U = w; p.O = y;
+  p.v_elems = (long long)batch * input_width; p.u_elems = (long long)input_width * units; p.o_elems = (long long)batch * units;
   p.P = batch; p.Q = units; p.K = input_width;
   dense_gather(p.g, input_width);
   p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = units; p.u_sq = 1;
@@ -1321,6 +1381,7 @@ int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w, co
   // the multiplier's FIRST operand, the gradient (lane operand here) the second.
   Params p{};
   p.V = g_; p.U = w; p.O = dx;
+  p.v_elems = (long long)batch * units; p.u_elems = (long long)input_width * units; p.o_elems = (long long)batch * input_width;
   p.P = batch; p.Q = input_width; p.K = units;
   dense_gather(p.g, units);
   p.u_t0 = 0; p.u_tj = 0; p.u_ti = 0; p.u_tap = 0; p.u_sk = 1; p.u_sq = units;
@@ -1332,6 +1393,7 @@ int amsim_dense_bwd_input(void* stream, const amsim_lut* lut, const float* w, co
 
 size_t amsim_dense_bwd_weight_workspace(int batch, int units, int input_width, unsigned flags) {
   if (batch <= 0 || units <= 0 || input_width <= 0) return 0;
+  if (units >= (1 << 30) || input_width >= (1 << 30) || (long long)batch >= (1ll << 31) - 256) return 0;  // refused by the op
   if (flags & AMSIM_INT32) return 0;
   const int sms = sm_count(current_device());
   if (wgrad_swap(input_width, units)) return fgrad_workspace(units, input_width, batch, flags & AMSIM_DETERMINISTIC, sms);
@@ -1383,6 +1445,8 @@ static int matmul_impl(void* stream, const amsim_lut* lut, const float* a, const
   if (!a || !b) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
   Params p{};
   p.V = a; p.U = b; p.O = c;
+  p.v_elems = (long long)(batch_a > 1 ? batch_a : 1) * row_a * col_a; p.u_elems = (long long)(batch_b > 1 ? batch_b : 1) * row_b * col_b;
+  p.o_elems = (long long)nb * M * N;
   p.P = M; p.Q = N; p.K = Ka;
   dense_gather(p.g, Ka);
   if (trans_a) {

@@ -113,6 +113,34 @@ struct Gather {
   FastDiv d_img, d_pw, d_sc, d_kw, d_dh, d_dw;
 };
 
+// Bounds-checking debug build (-DAMSIM_BOUNDS_CHECK; stands in for compute-sanitizer's memcheck):
+// every access of the kernels to a caller's tensor or to scratch is first compared with that
+// buffer's extent and natural alignment.  A bad access is NOT made: the first one is recorded
+// (source line, buffer, byte offset) in a device word the host reads back with
+// amsim_debug_bounds_report(), a bad load yields 0, a bad store is dropped, and the kernel carries
+// on, so the context stays usable.  In a normal build AMSIM_IN() is the constant true.
+constexpr int BUF_V = 0, BUF_U = 1, BUF_O = 2, BUF_WS = 3;
+#ifdef AMSIM_BOUNDS_CHECK
+struct Bounds {
+  const char* lo[4];
+  const char* hi[4];
+  unsigned long long* report;  // 0 = clean; else line << 44 | (buffer + 1) << 40 | low 40 bits of the byte offset
+};
+__device__ __noinline__ void amsim_bounds_record(const Bounds& b, int which, const void* p, int line) {
+  const unsigned long long off = (unsigned long long)((const char*)p - b.lo[which]) & ((1ull << 40) - 1);
+  atomicCAS(b.report, 0ull, ((unsigned long long)line << 44) | ((unsigned long long)(which + 1) << 40) | off);
+}
+__device__ __forceinline__ bool amsim_in(const Bounds& b, int which, const void* p, size_t bytes, int line) {
+  const char* a = (const char*)p;
+  if (a >= b.lo[which] && a + bytes <= b.hi[which] && ((uintptr_t)a & (bytes - 1)) == 0) return true;
+  amsim_bounds_record(b, which, p, line);
+  return false;
+}
+#define AMSIM_IN(prm_, which_, ptr_, type_) amsim_in((prm_).bnd, which_, ptr_, sizeof(type_), __LINE__)
+#else
+#define AMSIM_IN(prm_, which_, ptr_, type_) true
+#endif
+
 struct Params {
   const float* V;
   const float* U;
@@ -169,6 +197,10 @@ struct Params {
   int sk_ptiles, sk_qtiles;     // tile grid (q runs fastest, then p, then batch)
   int sk_grid;                  // CTAs of the balanced launch
   int* sk_count;                // per tile: CTAs that have parked their share (zero before the launch)
+  long long v_elems, u_elems, o_elems;  // extents of V, U and O in elements (bounds-checking build)
+#ifdef AMSIM_BOUNDS_CHECK
+  Bounds bnd;
+#endif
 };
 
 __device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
@@ -450,11 +482,11 @@ __device__ __forceinline__ void store_out_tile(const Params& prm, float (&acc)[T
         }
       }
       if (vec_out && qg + 3 < prm.Q) {
-        *reinterpret_cast<float4*>(orow + qg) = make_float4(o[0], o[1], o[2], o[3]);
+        if (AMSIM_IN(prm, BUF_O, orow + qg, float4)) *reinterpret_cast<float4*>(orow + qg) = make_float4(o[0], o[1], o[2], o[3]);
       } else {
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-          if (qg + r < prm.Q) orow[(long long)(qg + r) * prm.o_sq] = o[r];
+          if (qg + r < prm.Q && AMSIM_IN(prm, BUF_O, orow + (long long)(qg + r) * prm.o_sq, float)) orow[(long long)(qg + r) * prm.o_sq] = o[r];
       }
     }
   }
@@ -568,8 +600,9 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
             // only the deterministic input gradient gathers a stride-dilated tensor (fast mode runs
             // one sub-convolution per stride phase instead)
             const int row = EXACT ? (int)fdiv((uint32_t)u, g.d_dh) : u, col = EXACT ? (int)fdiv((uint32_t)v, g.d_dw) : v;
-            if (!EXACT || (row * g.dil_h == u && col * g.dil_w == v))
-              val = __ldg(reinterpret_cast<const float4*>(Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch)));
+            const float* src = Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch);
+            if ((!EXACT || (row * g.dil_h == u && col * g.dil_w == v)) && AMSIM_IN(prm, BUF_V, src, float4))
+              val = __ldg(reinterpret_cast<const float4*>(src));
           }
           vraw[ik][ip] = val;
         }
@@ -587,11 +620,12 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
             float val = 0.f;
             const int u = r0[ip] + kh, v = c0[ip] + kw;
             if (prm.v_trans) {
-              if (pv[ip] && kj < prm.K) val = __ldg(Vg + (long long)kj * prm.v_ld + (p0 + pl[ip]));
+              if (pv[ip] && kj < prm.K && AMSIM_IN(prm, BUF_V, Vg + (long long)kj * prm.v_ld + (p0 + pl[ip]), float))
+                val = __ldg(Vg + (long long)kj * prm.v_ld + (p0 + pl[ip]));
             } else if (pv[ip] && kj < prm.K && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
               const int row = EXACT ? (int)fdiv((uint32_t)u, g.d_dh) : u, col = EXACT ? (int)fdiv((uint32_t)v, g.d_dw) : v;
-              if (!EXACT || (row * g.dil_h == u && col * g.dil_w == v))
-                val = __ldg(Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch));
+              const float* src = Vg + nb[ip] + ((long long)(row * g.SW + col) * g.SC + ch);
+              if ((!EXACT || (row * g.dil_h == u && col * g.dil_w == v)) && AMSIM_IN(prm, BUF_V, src, float)) val = __ldg(src);
             }
             tmp[ip][j] = val;
           }
@@ -615,8 +649,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
           const int kk = kglob - (int)tap * g.SC;
           const int tj = (int)fdiv(tap, g.d_kw);
           const int tp = prm.u_t0 + tj * prm.u_tj + ((int)tap - tj * g.KW) * prm.u_ti;
-          val = __ldg(reinterpret_cast<const float4*>(Ug + (long long)tp * prm.u_tap + (long long)kk * prm.u_sk +
-                                                      (long long)qg * prm.u_sq));
+          const float* src = Ug + (long long)tp * prm.u_tap + (long long)kk * prm.u_sk + (long long)qg * prm.u_sq;
+          if (AMSIM_IN(prm, BUF_U, src, float4)) val = __ldg(reinterpret_cast<const float4*>(src));
         }
         uraw[4 * j] = val.x; uraw[4 * j + 1] = val.y; uraw[4 * j + 2] = val.z; uraw[4 * j + 3] = val.w;
       }
@@ -634,7 +668,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
         const int kk = kglob - (int)tap * g.SC;
         const int tj = (int)fdiv(tap, g.d_kw);
         const int tp = prm.u_t0 + tj * prm.u_tj + ((int)tap - tj * g.KW) * prm.u_ti;
-        val = __ldg(Ug + (long long)tp * prm.u_tap + (long long)kk * prm.u_sk + (long long)qg * prm.u_sq);
+        const float* src = Ug + (long long)tp * prm.u_tap + (long long)kk * prm.u_sk + (long long)qg * prm.u_sq;
+        if (AMSIM_IN(prm, BUF_U, src, float)) val = __ldg(src);
       }
       uraw[j] = val;
     }
@@ -799,7 +834,8 @@ AMSIM_UNROLL_K
 #pragma unroll
     for (int r = 0; r < TR; ++r)
 #pragma unroll
-      for (int c = 0; c < TC; ++c) __stcg(slot + (r * TC + c) * NT + t, acc[r][c]);
+      for (int c = 0; c < TC; ++c)
+        if (AMSIM_IN(prm, BUF_WS, slot + (r * TC + c) * NT + t, float)) __stcg(slot + (r * TC + c) * NT + t, acc[r][c]);
     __threadfence();  // this thread's part of the tile is visible device-wide before the count
     __syncthreads();
     const long long tile = ((long long)tile_z * prm.sk_ptiles + tile_p) * prm.sk_qtiles + tile_q;
@@ -811,7 +847,7 @@ AMSIM_UNROLL_K
     while (c1 > 0 && balanced_begin(c1, prm.sk_iters, prm.sk_grid) > last - 1) --c1;
     while (balanced_begin(c1 + 1, prm.sk_iters, prm.sk_grid) <= last - 1) ++c1;
     if (t == 0) {
-      const int arrived = atomicAdd(prm.sk_count + tile, 1);
+      const int arrived = AMSIM_IN(prm, BUF_WS, prm.sk_count + tile, int) ? atomicAdd(prm.sk_count + tile, 1) : 0;
       *flag_s = arrived == (int)(c1 - c0);  // c1 - c0 + 1 sharers
     }
     __syncthreads();
@@ -829,7 +865,8 @@ AMSIM_UNROLL_K
 #pragma unroll
         for (int r = 0; r < TR; ++r)
 #pragma unroll
-          for (int c = 0; c < TC; ++c) acc[r][c] = __fadd_rn(acc[r][c], __ldcg(src + (r * TC + c) * NT + t));
+          for (int c = 0; c < TC; ++c)
+            if (AMSIM_IN(prm, BUF_WS, src + (r * TC + c) * NT + t, float)) acc[r][c] = __fadd_rn(acc[r][c], __ldcg(src + (r * TC + c) * NT + t));
       }
       store_out_tile(prm, acc, Og, p0 + vcol, q0 + ucol);
     }
@@ -907,7 +944,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
         const float* src = Vg + (long long)n * ((long long)g.SH * g.SW * g.SC);
         if (VEC) {
           const int u = r0 + kh[0], v = c0 + kw[0];
-          if (pv[0] && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
+          if (pv[0] && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w &&
+              AMSIM_IN(prm, BUF_V, src + ((long long)(u * g.SW + v) * g.SC + ch[0]), float4))
             val = __ldg(reinterpret_cast<const float4*>(src + ((long long)(u * g.SW + v) * g.SC + ch[0])));
         } else {
           float tmp[4];
@@ -915,7 +953,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
           for (int j = 0; j < 4; ++j) {
             const int u = r0 + kh[j], v = c0 + kw[j];
             tmp[j] = 0.f;
-            if (pv[j] && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
+            if (pv[j] && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w &&
+                AMSIM_IN(prm, BUF_V, src + ((long long)(u * g.SW + v) * g.SC + ch[j]), float))
               tmp[j] = __ldg(src + ((long long)(u * g.SW + v) * g.SC + ch[j]));
           }
           val = make_float4(tmp[0], tmp[1], tmp[2], tmp[3]);
@@ -929,7 +968,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
         const int f = j * NT + t;
         const int pix = kbeg + kb * BK + (f >> 4), qg = q0 + (f & 15) * 4;
         float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (pix < kend && qg < prm.Q) val = __ldg(reinterpret_cast<const float4*>(Ug + (long long)pix * prm.u_sk + qg));
+        if (pix < kend && qg < prm.Q && AMSIM_IN(prm, BUF_U, Ug + (long long)pix * prm.u_sk + qg, float4))
+          val = __ldg(reinterpret_cast<const float4*>(Ug + (long long)pix * prm.u_sk + qg));
         uraw[4 * j] = val.x; uraw[4 * j + 1] = val.y; uraw[4 * j + 2] = val.z; uraw[4 * j + 3] = val.w;
       }
     } else {
@@ -937,7 +977,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
     for (int j = 0; j < NU; ++j) {
       const int e = j * NT + t;
       const int pix = kbeg + kb * BK + (e >> 6), qg = q0 + (e & 63);
-      uraw[j] = (pix < kend && qg < prm.Q) ? __ldg(Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq) : 0.f;
+      const float* src = Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq;
+      uraw[j] = (pix < kend && qg < prm.Q && AMSIM_IN(prm, BUF_U, src, float)) ? __ldg(src) : 0.f;
     }
     }
   };
@@ -1040,12 +1081,14 @@ AMSIM_UNROLL_K
     for (int g4 = 0; g4 < TR / 4; ++g4) {
       const int qg = q0 + ucol + 4 * g4;
       if (vec_out && qg + 3 < prm.Q) {
-        *reinterpret_cast<float4*>(orow + qg) =
-            make_float4(acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]);
+        if (AMSIM_IN(prm, to_ws ? BUF_WS : BUF_O, orow + qg, float4))
+          *reinterpret_cast<float4*>(orow + qg) =
+              make_float4(acc[4 * g4][c], acc[4 * g4 + 1][c], acc[4 * g4 + 2][c], acc[4 * g4 + 3][c]);
       } else {
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-          if (qg + r < prm.Q) orow[(long long)(qg + r) * sq] = acc[4 * g4 + r][c];
+          if (qg + r < prm.Q && AMSIM_IN(prm, to_ws ? BUF_WS : BUF_O, orow + (long long)(qg + r) * sq, float))
+            orow[(long long)(qg + r) * sq] = acc[4 * g4 + r][c];
       }
     }
   }
@@ -1104,8 +1147,8 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
         const uint32_t a = fdiv(rem, g.d_pw);
         const uint32_t b = rem - a * (uint32_t)g.PW;
         const int u = (int)a * g.ps_h - g.off_t + kh, v = (int)b * g.ps_w - g.off_l + kw;
-        if ((unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
-          val = __ldg(Vg + (long long)n * ((long long)g.SH * g.SW * g.SC) + ((long long)(u * g.SW + v) * g.SC + ch));
+        const float* src = Vg + (long long)n * ((long long)g.SH * g.SW * g.SC) + ((long long)(u * g.SW + v) * g.SC + ch);
+        if ((unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w && AMSIM_IN(prm, BUF_V, src, float)) val = __ldg(src);
       }
       vraw[i] = val;
     }
@@ -1113,8 +1156,8 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
     for (int j = 0; j < NUQ; ++j) {
       const int e = j * NT + t;
       const int pix = kbeg + kb * BK + e / BQT, qg = q0 + e % BQT;
-      uraw[j] = (e < BK * BQT && pix < kend && qg < prm.Q)
-                    ? __ldg(Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq) : 0.f;
+      const float* src = Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq;
+      uraw[j] = (e < BK * BQT && pix < kend && qg < prm.Q && AMSIM_IN(prm, BUF_U, src, float)) ? __ldg(src) : 0.f;
     }
   };
   auto store_tile = [&](int buf) {
@@ -1179,8 +1222,9 @@ __global__ void __launch_bounds__(32 * NW) fgrad_exact_thin(const Params prm) {
     for (int r = 0; r < TQ; ++r) {
       const int qg = q0 + w * TQ + r;
       if (qg < prm.Q) {
-        if (prm.splits > 1) prm.ws[((long long)blockIdx.z * prm.P + pg) * prm.Q + qg] = acc[r];
-        else prm.O[(long long)pg * prm.o_sp + (long long)qg * prm.o_sq] = acc[r];
+        float* dst = prm.splits > 1 ? prm.ws + (((long long)blockIdx.z * prm.P + pg) * prm.Q + qg)
+                                    : prm.O + ((long long)pg * prm.o_sp + (long long)qg * prm.o_sq);
+        if (AMSIM_IN(prm, prm.splits > 1 ? BUF_WS : BUF_O, dst, float)) *dst = acc[r];
       }
     }
   }
@@ -1241,15 +1285,16 @@ __global__ void __launch_bounds__(768) fgrad_exact_chain(const Params prm) {
         const uint32_t a = fdiv(rem, g.d_pw);
         const uint32_t b = rem - a * (uint32_t)g.PW;
         const int u = (int)a * g.ps_h - g.off_t + kh, v = (int)b * g.ps_w - g.off_l + kw;
-        if ((unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w)
-          val = __ldg(Vg + (long long)n * ((long long)g.SH * g.SW * g.SC) + ((long long)(u * g.SW + v) * g.SC + ch));
+        const float* src = Vg + (long long)n * ((long long)g.SH * g.SW * g.SC) + ((long long)(u * g.SW + v) * g.SC + ch);
+        if ((unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w && AMSIM_IN(prm, BUF_V, src, float)) val = __ldg(src);
       }
       vraw[0] = val;
     }
     uraw = 0.f;
     if (t < BK * BQT) {
       const int pix = kb * BK + (t >> 3), qg = q0 + (t & 7);
-      if (pix < prm.K && qg < prm.Q) uraw = __ldg(Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq);
+      const float* src = Ug + (long long)pix * prm.u_sk + (long long)qg * prm.u_sq;
+      if (pix < prm.K && qg < prm.Q && AMSIM_IN(prm, BUF_U, src, float)) uraw = __ldg(src);
     }
   };
   auto store_tile = [&](int buf, const float (&vraw)[1], float uraw) {
@@ -1320,7 +1365,8 @@ __global__ void __launch_bounds__(768) fgrad_exact_chain(const Params prm) {
     }
   }
   const int qg = q0 + wc;
-  if (!producer && pv && qg < prm.Q) prm.O[(long long)pg * prm.o_sp + (long long)qg * prm.o_sq] = acc;
+  if (!producer && pv && qg < prm.Q && AMSIM_IN(prm, BUF_O, prm.O + ((long long)pg * prm.o_sp + (long long)qg * prm.o_sq), float))
+    prm.O[(long long)pg * prm.o_sp + (long long)qg * prm.o_sq] = acc;
 }
 
 // Sums the split-K partials in ascending split order (fixed order: the result

@@ -111,6 +111,17 @@ class _DenseamBiasActFn(torch.autograd.Function):
         return dx, dw, db, None, None, None
 
 
+def _unbroadcast(grad, operand):
+    """Gradient of an operand that MatMulAM broadcast over the batch: a rank-2 operand, or a
+    rank-3 operand whose batch is 1 against a larger batch (matmulam.cc:86-147).  The per-batch
+    gradients are summed (exact FP32 adds) back to the operand's shape."""
+    if operand.dim() == 2 and grad.dim() == 3:
+        return grad.sum(0)
+    if operand.dim() == 3 and grad.dim() == 3 and operand.shape[0] == 1 and grad.shape[0] > 1:
+        return grad.sum(0, keepdim=True)
+    return grad
+
+
 class _MatMulAMFn(torch.autograd.Function):
     """C = alpha * op(A) @ op(B).  Gradients follow the four transpose cases of the
     reference's registered gradient (python/ops/math_ops.py:127-157), every product
@@ -135,15 +146,13 @@ class _MatMulAMFn(torch.autograd.Function):
                 da = ops.matmulam(g, b, transpose_b=not tb, **kw)
             else:
                 da = ops.matmulam(b, g, transpose_a=tb, transpose_b=True, **kw)
-            if a.dim() == 2 and da.dim() == 3:
-                da = da.sum(0)
+            da = _unbroadcast(da, a)
         if ctx.needs_input_grad[1]:
             if not tb:
                 db = ops.matmulam(a, g, transpose_a=not ta, **kw)
             else:
                 db = ops.matmulam(g, a, transpose_a=True, transpose_b=ta, **kw)
-            if b.dim() == 2 and db.dim() == 3:
-                db = db.sum(0)
+            db = _unbroadcast(db, b)
         return da, db, None, None, None, None, None
 
 

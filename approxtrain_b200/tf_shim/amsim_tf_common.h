@@ -8,6 +8,8 @@
 #define AMSIM_TF_COMMON_H_
 
 #define EIGEN_USE_GPU
+#include <stdlib.h>
+
 #include <string>
 
 #include "amsim.h"
@@ -44,6 +46,18 @@ class LutAttr {
  private:
   amsim_lut* lut_ = nullptr;
 };
+
+// AMSIM_FAST unless the process environment holds AMSIM_TF_DETERMINISTIC=1 when the first op runs:
+// then every op takes the reference's exact summation order (AMSIM_DETERMINISTIC), bit-identical
+// to the reference's GPU kernels.  Read once; the ops are registered for T = float only (the
+// reference's int32 registrations are served by the C ABI's AMSIM_INT32 flag, not by these hosts).
+inline unsigned ModeFlag() {
+  static const unsigned flag = [] {
+    const char* e = getenv("AMSIM_TF_DETERMINISTIC");
+    return (e && *e && *e != '0') ? (unsigned)AMSIM_DETERMINISTIC : (unsigned)AMSIM_FAST;
+  }();
+  return flag;
+}
 
 inline void* StreamOf(OpKernelContext* ctx) {
   return reinterpret_cast<void*>(ctx->eigen_device<Eigen::GpuDevice>().stream());

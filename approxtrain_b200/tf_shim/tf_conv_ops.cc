@@ -10,6 +10,7 @@
 using namespace tensorflow;  // NOLINT
 using amsim_tf::FromAmsim;
 using amsim_tf::LutAttr;
+using amsim_tf::ModeFlag;
 using amsim_tf::StreamOf;
 
 namespace {
@@ -127,7 +128,7 @@ class AmsimConvOp : public OpKernel {
     OP_REQUIRES_OK(ctx, FromAmsim(amsim_conv2d_fwd(StreamOf(ctx), lut_.get(), x.flat<float>().data(),
                                                    f.flat<float>().data(), y->flat<float>().data(), g.n, g.h, g.w, g.c,
                                                    g.kh, g.kw, g.k, g.oh, g.ow, win_.stride_h, win_.stride_w, g.pt,
-                                                   g.pl, AMSIM_FAST)));
+                                                   g.pl, ModeFlag())));
   }
 
  private:
@@ -155,7 +156,7 @@ class AmsimConvInputGradOp : public OpKernel {
     OP_REQUIRES_OK(ctx, FromAmsim(amsim_conv2d_bwd_input(StreamOf(ctx), lut_.get(), f.flat<float>().data(),
                                                          dy.flat<float>().data(), dx->flat<float>().data(), g.n, g.h,
                                                          g.w, g.c, g.kh, g.kw, g.k, g.oh, g.ow, win_.stride_h,
-                                                         win_.stride_w, g.pt, g.pl, AMSIM_FAST)));
+                                                         win_.stride_w, g.pt, g.pl, ModeFlag())));
   }
 
  private:
@@ -179,7 +180,7 @@ class AmsimConvFilterGradOp : public OpKernel {
     Geometry g;
     OP_REQUIRES_OK(ctx, MakeGeometry(win_, x.shape(), f_shape, &g));
     const size_t ws_bytes =
-        amsim_conv2d_bwd_filter_workspace(g.n, g.h, g.w, g.c, g.kh, g.kw, g.k, g.oh, g.ow, AMSIM_FAST);
+        amsim_conv2d_bwd_filter_workspace(g.n, g.h, g.w, g.c, g.kh, g.kw, g.k, g.oh, g.ow, ModeFlag());
     Tensor ws;
     void* ws_ptr = nullptr;
     if (ws_bytes > 0) {
@@ -190,7 +191,7 @@ class AmsimConvFilterGradOp : public OpKernel {
     OP_REQUIRES_OK(ctx, FromAmsim(amsim_conv2d_bwd_filter(StreamOf(ctx), lut_.get(), x.flat<float>().data(),
                                                           dy.flat<float>().data(), dw->flat<float>().data(), g.n, g.h,
                                                           g.w, g.c, g.kh, g.kw, g.k, g.oh, g.ow, win_.stride_h,
-                                                          win_.stride_w, g.pt, g.pl, ws_ptr, ws_bytes, AMSIM_FAST)));
+                                                          win_.stride_w, g.pt, g.pl, ws_ptr, ws_bytes, ModeFlag())));
   }
 
  private:

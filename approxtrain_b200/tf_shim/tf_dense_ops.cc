@@ -7,6 +7,7 @@
 using namespace tensorflow;  // NOLINT
 using amsim_tf::FromAmsim;
 using amsim_tf::LutAttr;
+using amsim_tf::ModeFlag;
 using amsim_tf::StreamOf;
 
 REGISTER_OP("Denseam")
@@ -46,7 +47,7 @@ class AmsimDenseOp : public OpKernel {
     if (y->NumElements() == 0) return;
     OP_REQUIRES_OK(ctx, FromAmsim(amsim_dense_fwd(StreamOf(ctx), lut_.get(), x.flat<float>().data(),
                                                   w.flat<float>().data(), y->flat<float>().data(), batch, units, width,
-                                                  AMSIM_FAST)));
+                                                  ModeFlag())));
   }
 
  private:
@@ -66,7 +67,7 @@ class AmsimDenseGradOp : public OpKernel {
     Tensor *dx = nullptr, *dw = nullptr;
     OP_REQUIRES_OK(ctx, ctx->allocate_output(0, x.shape(), &dx));
     OP_REQUIRES_OK(ctx, ctx->allocate_output(1, w.shape(), &dw));
-    const size_t ws_bytes = amsim_dense_bwd_weight_workspace(batch, units, width, AMSIM_FAST);
+    const size_t ws_bytes = amsim_dense_bwd_weight_workspace(batch, units, width, ModeFlag());
     Tensor ws;
     void* ws_ptr = nullptr;
     if (ws_bytes > 0) {
@@ -76,10 +77,10 @@ class AmsimDenseGradOp : public OpKernel {
     }
     OP_REQUIRES_OK(ctx, FromAmsim(amsim_dense_bwd_weight(StreamOf(ctx), lut_.get(), x.flat<float>().data(),
                                                          g.flat<float>().data(), dw->flat<float>().data(), batch, units,
-                                                         width, ws_ptr, ws_bytes, AMSIM_FAST)));
+                                                         width, ws_ptr, ws_bytes, ModeFlag())));
     OP_REQUIRES_OK(ctx, FromAmsim(amsim_dense_bwd_input(StreamOf(ctx), lut_.get(), w.flat<float>().data(),
                                                         g.flat<float>().data(), dx->flat<float>().data(), batch, units,
-                                                        width, AMSIM_FAST)));
+                                                        width, ModeFlag())));
   }
 
  private:

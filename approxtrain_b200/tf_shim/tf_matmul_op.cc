@@ -18,6 +18,7 @@
 using namespace tensorflow;  // NOLINT
 using amsim_tf::FromAmsim;
 using amsim_tf::LutAttr;
+using amsim_tf::ModeFlag;
 using amsim_tf::StreamOf;
 
 static Status MatMulAMShape(shape_inference::InferenceContext* c) {
@@ -98,7 +99,7 @@ class AmsimMatMulOp : public OpKernel {
     OP_REQUIRES_OK(ctx, FromAmsim(amsim_matmul_ex(StreamOf(ctx), lut_.get(), a.flat<float>().data(),
                                                   b.flat<float>().data(), out->flat<float>().data(), ba, bb, row_a,
                                                   col_a, row_b, col_b, ta_ ? 1 : 0, tb_ ? 1 : 0, /*alpha=*/nullptr,
-                                                  AMSIM_FAST)));
+                                                  ModeFlag())));
   }
 
  private:

@@ -281,6 +281,15 @@ unsigned long long amsim_debug_launch_count(void);
  * threads.  No reference counterpart. */
 void amsim_debug_reload_env(void);
 
+/* Bounds-checking debug build (compiled with -DAMSIM_BOUNDS_CHECK; the stand-in for a device-side
+ * memory checker): every access of the kernels to a caller's tensor or to scratch is compared with
+ * the buffer's extent and alignment before it is made; a bad one is skipped and the first is
+ * recorded.  This call waits for the device, returns that record in *word (0 = every access since
+ * the last call was in bounds; otherwise source line << 44 | (buffer + 1) << 40 | byte offset, buffers
+ * 0 lane operand, 1 uniform operand, 2 output, 3 scratch) and clears it.  A normal build returns
+ * AMSIM_ERR_UNSUPPORTED and *word = 0.  No reference counterpart. */
+int amsim_debug_bounds_report(unsigned long long* word);
+
 /* Host-side check of the kernels' constant-divisor arithmetic (no GPU work):
  * returns n / d computed the way the device code does.  For tests. */
 uint32_t amsim_debug_fastdiv(uint32_t n, uint32_t d);

@@ -6,6 +6,7 @@
 #   oracle/_ref/lut/*.bin          output of the reference's lut/lut_gen.cc
 #   oracle/_ref/lut/MBM_11.bin     m = 11 LUT from cuda/FPmultMBM_fast32.inl
 #   oracle/_ref/libref_model_<LUT>.so   the functional model each shipped LUT was generated from
+#   oracle/_ref/libref_cuda.so     the reference's GPU kernels and launchers (oracle/build_ref_cuda.sh)
 # Reference sources are compiled where they lie; nothing is copied.
 # Usage: oracle/build.sh [reference_dir]
 # (default: $AMSIM_REFERENCE_DIR, else the directory "reference" beside this repository)
@@ -40,6 +41,8 @@ if [ -f "$ref/cuda/AMsimulator.inl" ]; then
   "$tmp/gen_lut_m11" "$here/_ref/lut/MBM_11.bin"
   rm -rf "$tmp"
   echo "oracle/_ref built from $ref"
+  # the reference's own GPU kernels and launchers, for the GPU tests (needs nvcc)
+  bash "$here/build_ref_cuda.sh" "$ref"
 else
   echo "no reference checkout at $ref: oracle/_ref not rebuilt"
 fi

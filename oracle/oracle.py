@@ -302,3 +302,85 @@ class RefModel:
         out = np.empty_like(at)
         self.lib.ref_model_mul_array(at, bt, out, at.size)
         return out
+
+
+class RefCuda:
+    """The reference's own GPU functors, compiled unmodified from a reference checkout by
+    oracle/build_ref_cuda.sh (oracle/_ref/libref_cuda.so).  Takes and returns torch CUDA
+    tensors; every call synchronises the device, as the reference does.  Checker only."""
+
+    _LIB = os.path.join(_HERE, "_ref", "libref_cuda.so")
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(RefCuda._LIB)
+
+    def __init__(self, lut_path: str):
+        L = self.lib = C.CDLL(self._LIB)
+        vp, ip = C.c_void_p, C.c_int
+        L.ref_cuda_lut_open.argtypes = [C.c_char_p]
+        L.ref_cuda_lut_open.restype = vp
+        L.ref_cuda_lut_close.argtypes = [vp]
+        L.ref_cuda_conv2d_fwd.argtypes = [vp] * 5 + [ip] * 14
+        L.ref_cuda_conv2d_bwd_filter.argtypes = [vp] * 5 + [ip] * 13
+        L.ref_cuda_conv2d_bwd_input.argtypes = [vp] * 6 + [ip] * 13
+        for n in ("ref_cuda_dense_fwd", "ref_cuda_dense_bwd_weight", "ref_cuda_dense_bwd_input"):
+            getattr(L, n).argtypes = [vp] * 4 + [ip] * 3
+        L.ref_cuda_matmul.argtypes = [vp] * 4 + [ip] * 6
+        self.h = L.ref_cuda_lut_open(lut_path.encode())
+
+    def close(self):
+        if self.h:
+            self.lib.ref_cuda_lut_close(self.h)
+            self.h = None
+
+    @staticmethod
+    def _p(t):
+        return C.c_void_p(t.data_ptr())
+
+    def conv2d_fwd(self, g: ConvGeom, x, w, same: bool):
+        import torch
+        y = torch.empty((g.batch, g.out_h, g.out_w, g.out_c), dtype=torch.float32, device=x.device)
+        col = torch.empty(g.batch * g.out_h * g.out_w * g.f_h * g.f_w * g.in_c, dtype=torch.float32, device=x.device)
+        self.lib.ref_cuda_conv2d_fwd(self.h, self._p(x), self._p(w), self._p(y), self._p(col), g.batch, g.in_h, g.in_w, g.in_c,
+                                     g.f_h, g.f_w, g.out_c, g.out_h, g.out_w, g.stride_h, g.stride_w, g.pad_top, g.pad_left,
+                                     2 if same else 1)   # tensorflow::Padding: VALID = 1, SAME = 2 (convam.cc:557)
+        return y
+
+    def conv2d_bwd_filter(self, g: ConvGeom, x, dy):
+        import torch
+        dw = torch.empty((g.f_h, g.f_w, g.in_c, g.out_c), dtype=torch.float32, device=x.device)
+        col = torch.empty(g.batch * g.out_h * g.out_w * g.f_h * g.f_w * g.in_c, dtype=torch.float32, device=x.device)
+        self.lib.ref_cuda_conv2d_bwd_filter(self.h, self._p(x), self._p(dy), self._p(dw), self._p(col), g.batch, g.in_h, g.in_w,
+                                            g.in_c, g.f_h, g.f_w, g.out_c, g.out_h, g.out_w, g.stride_h, g.stride_w,
+                                            g.pad_top, g.pad_left)
+        return dw
+
+    def conv2d_bwd_input(self, g: ConvGeom, w, dy):
+        import torch
+        dx = torch.empty((g.batch, g.in_h, g.in_w, g.in_c), dtype=torch.float32, device=w.device)
+        col = torch.empty(g.batch * g.in_h * g.in_w * g.f_h * g.f_w * g.out_c, dtype=torch.float32, device=w.device)
+        rs = torch.empty(g.f_h * g.f_w * g.in_c * g.out_c, dtype=torch.float32, device=w.device)
+        self.lib.ref_cuda_conv2d_bwd_input(self.h, self._p(w), self._p(dy), self._p(dx), self._p(col), self._p(rs), g.batch,
+                                           g.in_h, g.in_w, g.in_c, g.f_h, g.f_w, g.out_c, g.out_h, g.out_w, g.stride_h,
+                                           g.stride_w, g.pad_top, g.pad_left)
+        return dx
+
+    def dense(self, which, p, q, batch, units, in_w):
+        import torch
+        shape = {"fwd": (batch, units), "bwd_weight": (in_w, units), "bwd_input": (batch, in_w)}[which]
+        out = torch.empty(shape, dtype=torch.float32, device=p.device)
+        getattr(self.lib, "ref_cuda_dense_" + which)(self.h, self._p(p), self._p(q), self._p(out), batch, units, in_w)
+        return out
+
+    def matmul(self, a, b):
+        """Ranks (2,2), (3,3), (2,3), (3,2); a batch of 0 marks a rank-2 operand (matmulam.cc:86-147)."""
+        import torch
+        ba = a.shape[0] if a.dim() == 3 else 0
+        bb = b.shape[0] if b.dim() == 3 else 0
+        nb = max(ba, bb)
+        m, n = a.shape[-2], b.shape[-1]
+        out = torch.empty((nb, m, n) if nb else (m, n), dtype=torch.float32, device=a.device)
+        self.lib.ref_cuda_matmul(self.h, self._p(a), self._p(b), self._p(out), ba, bb, a.shape[-2], a.shape[-1], b.shape[-2],
+                                 b.shape[-1])
+        return out

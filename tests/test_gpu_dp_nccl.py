@@ -38,7 +38,7 @@ def _net(which, dev):
     return LeNet5(lut_path("MIT_7")).to(dev)
 
 
-def _worker(rank, world, port, out, which):
+def _worker(rank, world, port, out, which, graph=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
@@ -50,19 +50,26 @@ def _worker(rank, world, port, out, which):
     x, y = _data(which)
     n = x.shape[0] // world
     xs, ys = x[rank * n:(rank + 1) * n].to(dev), y[rank * n:(rank + 1) * n].to(dev)
-    for _ in range(2):
-        tr.step(lambda: torch.nn.functional.cross_entropy(net(xs), ys))
+    fn = lambda: torch.nn.functional.cross_entropy(net(xs), ys)
+    if graph:
+        # one eager warm-up step, then the step replayed from CUDA graphs (forward + backward captured,
+        # all-reduce between the graphs, update captured): two steps in all, like the eager run
+        replay = tr.capture(fn, warmup=1)
+        replay()
+    else:
+        for _ in range(2):
+            tr.step(fn)
     torch.cuda.synchronize()
     torch.save([p.detach().cpu() for p in net.parameters()], os.path.join(out, f"rank{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("which", ["lenet300100", "lenet5"])
-def test_two_gpus_give_the_full_batch_update(tmp_path, which):
+@pytest.mark.parametrize("which,graph", [("lenet300100", False), ("lenet5", False), ("lenet5", True)])
+def test_two_gpus_give_the_full_batch_update(tmp_path, which, graph):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), which), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), which, graph), nprocs=2, join=True)
     r0 = torch.load(tmp_path / "rank0.pt")
     r1 = torch.load(tmp_path / "rank1.pt")
     for a, b in zip(r0, r1):
@@ -80,4 +87,5 @@ def test_two_gpus_give_the_full_batch_update(tmp_path, which):
     for a, p in zip(r0, net.parameters()):
         worst = max(worst, float((a - p.detach().cpu()).abs().max()))
         assert torch.allclose(a, p.detach().cpu(), atol=1e-6, rtol=1e-4)
-    print(f"{which}: replicas identical on 2 GPUs; max |sharded - full batch| over all parameters {worst:.3e}")
+    print(f"{which}{' (CUDA graphs)' if graph else ''}: replicas identical on 2 GPUs; "
+          f"max |sharded - full batch| over all parameters {worst:.3e}")

@@ -93,6 +93,32 @@ def test_matmul_gradient_wiring(oracle, luts):
     assert beq(b.grad.cpu().numpy().reshape(6, 5, 7), oracle.matmul(np.ascontiguousarray(an.transpose(0, 2, 1)), gn, lut, m))
 
 
+@pytest.mark.parametrize("sa,sb", [((1, 8, 5), (4, 5, 7)), ((4, 8, 5), (1, 5, 7)), ((8, 5), (4, 5, 7)), ((4, 8, 5), (5, 7))])
+def test_matmul_gradient_of_a_broadcast_operand(oracle, luts, sa, sb):
+    """An operand that MatMulAM broadcasts over the batch (rank 2, or rank 3 with batch 1) gets the
+    sum of the per-batch gradients, in its own shape."""
+    from approxtrain_b200.layers import ammatmul
+    lut, m = luts["MBM_7"]
+    rng = np.random.default_rng(26)
+    an, bn = rng.standard_normal(sa).astype(np.float32), rng.standard_normal(sb).astype(np.float32)
+    a = torch.from_numpy(an).cuda().requires_grad_()
+    b = torch.from_numpy(bn).cuda().requires_grad_()
+    c = ammatmul(a, b, lut_path("MBM_7"), True)
+    gn = rng.standard_normal(tuple(c.shape)).astype(np.float32)
+    c.backward(torch.from_numpy(gn).cuda())
+    assert a.grad.shape == a.shape and b.grad.shape == b.shape
+    nb = gn.shape[0]
+    af = np.broadcast_to(an.reshape(-1, *an.shape[-2:]), (nb, *an.shape[-2:])).copy()
+    bf = np.broadcast_to(bn.reshape(-1, *bn.shape[-2:]), (nb, *bn.shape[-2:])).copy()
+    T = lambda x: np.ascontiguousarray(x.transpose(0, 2, 1))
+    da = torch.from_numpy(oracle.matmul(gn, T(bf), lut, m))
+    db = torch.from_numpy(oracle.matmul(T(af), gn, lut, m))
+    want_a = da.sum(0).reshape(sa) if (len(sa) == 2 or sa[0] == 1) else da
+    want_b = db.sum(0).reshape(sb) if (len(sb) == 2 or sb[0] == 1) else db
+    assert rel_l2(a.grad.cpu().numpy(), want_a.numpy()) <= 1e-6
+    assert rel_l2(b.grad.cpu().numpy(), want_b.numpy()) <= 1e-6
+
+
 @pytest.mark.parametrize("ta,tb", [(False, True), (True, False), (True, True)])
 def test_matmul_gradient_wiring_with_transposes_and_alpha(oracle, luts, ta, tb):
     """The four transpose cases of the reference's MatMulAM gradient (math_ops.py:127-157),
