@@ -26,7 +26,7 @@ EXPORTS = [
     "amsim_conv2d_bwd_filter_workspace", "amsim_conv2d_bwd_filter", "amsim_conv2d_bwd_filter_static",
     "amsim_dense_fwd",
     "amsim_dense_bwd_weight_workspace", "amsim_dense_bwd_weight", "amsim_dense_bwd_input", "amsim_matmul",
-    "amsim_matmul_ex",
+    "amsim_matmul_ex", "amsim_bias_grad_workspace", "amsim_bias_grad",
     "amsim_debug_fastdiv", "amsim_debug_launch_count", "amsim_debug_reload_env", "amsim_debug_bounds_report",
 ]
 
@@ -70,6 +70,9 @@ def _load() -> C.CDLL:
     L.amsim_dense_bwd_input.argtypes = [vp, vp, fp, fp, fp, ip, ip, ip, u]
     L.amsim_matmul.argtypes = [vp, vp, fp, fp, fp] + [ip] * 6 + [u]
     L.amsim_matmul_ex.argtypes = [vp, vp, fp, fp, fp] + [ip] * 8 + [C.POINTER(C.c_float), u]
+    L.amsim_bias_grad_workspace.argtypes = [C.c_longlong, ip]
+    L.amsim_bias_grad_workspace.restype = sz
+    L.amsim_bias_grad.argtypes = [vp, fp, fp, C.c_longlong, ip, vp, sz]
     L.amsim_debug_fastdiv.argtypes = [C.c_uint32, C.c_uint32]
     L.amsim_debug_fastdiv.restype = C.c_uint32
     L.amsim_debug_launch_count.argtypes = []

@@ -1324,6 +1324,69 @@ int amsim_conv2d_bwd_filter_static(void* stream, const amsim_lut* lut, const flo
                                  stride_h, stride_w, pad_top, pad_left, scratch, need, flags);
 }
 
+// ---- bias gradient ------------------------------------------------------------------------------
+// How the rows of a rows x cols gradient are cut into chunks: enough blocks to fill the device
+// about four times over, at least 64 rows per chunk.
+static void bias_grad_plan(long long rows, int cols, int sms, bool vec, int* cg, int* col_tiles, long long* chunks,
+                           long long* rows_per_chunk) {
+  const int groups = vec ? cols / 4 : cols;
+  int c = 1;
+  while (c < 64 && c < groups) c <<= 1;   // column groups per block: a power of two, at most 64
+  *cg = c;
+  *col_tiles = (groups + c - 1) / c;
+  long long want = (4ll * sms + *col_tiles - 1) / *col_tiles;
+  const long long most = (rows + 63) / 64;
+  if (want > most) want = most;
+  if (want < 1) want = 1;
+  *rows_per_chunk = (rows + want - 1) / want;
+  *chunks = (rows + *rows_per_chunk - 1) / *rows_per_chunk;
+}
+
+size_t amsim_bias_grad_workspace(long long rows, int cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  int cg, tiles;
+  long long chunks, rpc;
+  bias_grad_plan(rows, cols, sm_count(current_device()), cols % 4 == 0, &cg, &tiles, &chunks, &rpc);
+  long long scalar_chunks;
+  bias_grad_plan(rows, cols, sm_count(current_device()), false, &cg, &tiles, &scalar_chunks, &rpc);
+  const long long most = chunks > scalar_chunks ? chunks : scalar_chunks;  // the launch may fall back to scalar loads
+  return most > 1 ? (size_t)most * cols * sizeof(float) : 0;
+}
+
+int amsim_bias_grad(void* stream, const float* grad, float* dbias, long long rows, int cols, void* workspace,
+                    size_t workspace_bytes) {
+  if (rows < 0 || cols <= 0) return fail(AMSIM_ERR_INVALID, "bias gradient: rows >= 0 and cols > 0 expected");
+  if (!dbias) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows == 0) {
+    CUDA_TRY(cudaMemsetAsync(dbias, 0, sizeof(float) * (size_t)cols, st));
+    return AMSIM_OK;
+  }
+  if (!grad) return fail(AMSIM_ERR_INVALID, "NULL tensor pointer");
+  const bool vec = cols % 4 == 0 && aligned16(grad);
+  int cg, tiles;
+  long long chunks, rpc;
+  bias_grad_plan(rows, cols, sm_count(current_device()), vec, &cg, &tiles, &chunks, &rpc);
+  float* part = dbias;
+  if (chunks > 1) {
+    const size_t need = (size_t)chunks * cols * sizeof(float);
+    if (!workspace || workspace_bytes < need)
+      return fail(AMSIM_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, workspace ? workspace_bytes : (size_t)0);
+    part = static_cast<float*>(workspace);
+  }
+  dim3 grid((unsigned)chunks, (unsigned)tiles);
+  AMSIM_COUNT_LAUNCH();
+  if (vec) column_sums<true><<<grid, 256, 0, st>>>(grad, part, rows, cols, rpc, cg);
+  else column_sums<false><<<grid, 256, 0, st>>>(grad, part, rows, cols, rpc, cg);
+  CUDA_TRY(cudaGetLastError());
+  if (chunks > 1) {
+    AMSIM_COUNT_LAUNCH();
+    reduce_splits<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(part, dbias, cols, (int)chunks, cols, 0, 1);
+    CUDA_TRY(cudaGetLastError());
+  }
+  return AMSIM_OK;
+}
+
 static void dense_gather(Gather& g, int width) {
   g.PH = 1; g.PW = 1; g.ps_h = 1; g.ps_w = 1; g.off_t = 0; g.off_l = 0; g.lim_h = 1; g.lim_w = 1;
   g.dil_h = 1; g.dil_w = 1; g.SH = 1; g.SW = 1; g.SC = width; g.KW = 1;

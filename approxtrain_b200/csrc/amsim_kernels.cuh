@@ -1382,6 +1382,53 @@ __global__ void reduce_splits(const float* __restrict__ ws, float* __restrict__ 
   out[p * o_sp + q * o_sq] = s;
 }
 
+// -----------------------------------------------------------------------------
+// column_sums: part[chunk][c] = sum over the chunk's rows of g[row][c], exact FP32 adds.
+// The bias gradient of a layer (sum of the output gradient over every pixel / sample) - an exact
+// op that sits between the AM ops of a training step and is bound by one read of the gradient
+// from HBM.  grid = (chunks, ceil(col groups / CG)); a block of 256 threads covers CG column
+// groups (VEC: 4 columns each, 128-bit loads) x 256 / CG rows per pass; every thread adds the rows
+// it visits in ascending order, the block's threads of one column group are then added in thread
+// order through shared memory, and reduce_splits adds the chunks in ascending order: the result
+// does not depend on scheduling.
+// -----------------------------------------------------------------------------
+template <bool VEC>
+__global__ void __launch_bounds__(256) column_sums(const float* __restrict__ g, float* __restrict__ part, long long rows,
+                                                   int cols, long long rows_per_chunk, int CG) {
+  constexpr int W = VEC ? 4 : 1;
+  __shared__ float red[256 * W];
+  const int groups = (cols + W - 1) / W;
+  const int cg = threadIdx.x % CG, rl = threadIdx.x / CG, RL = 256 / CG;
+  const int grp = blockIdx.y * CG + cg;
+  const long long r0 = (long long)blockIdx.x * rows_per_chunk;
+  const long long r1 = min(rows, r0 + rows_per_chunk);
+  float acc[W];
+#pragma unroll
+  for (int i = 0; i < W; ++i) acc[i] = 0.f;
+  if (grp < groups) {
+    for (long long r = r0 + rl; r < r1; r += RL) {
+      if (VEC) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(g + r * cols) + grp);
+        acc[0] = __fadd_rn(acc[0], v.x); acc[1 % W] = __fadd_rn(acc[1 % W], v.y);
+        acc[2 % W] = __fadd_rn(acc[2 % W], v.z); acc[3 % W] = __fadd_rn(acc[3 % W], v.w);
+      } else {
+        acc[0] = __fadd_rn(acc[0], __ldg(g + r * cols + grp));
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < W; ++i) red[(rl * CG + cg) * W + i] = acc[i];
+  __syncthreads();
+  if (rl == 0 && grp < groups) {
+    for (int j = 1; j < RL; ++j)
+#pragma unroll
+      for (int i = 0; i < W; ++i) acc[i] = __fadd_rn(acc[i], red[(j * CG + cg) * W + i]);
+#pragma unroll
+    for (int i = 0; i < W; ++i)
+      if (grp * W + i < cols) part[(long long)blockIdx.x * cols + grp * W + i] = acc[i];
+  }
+}
+
 // The reference primitive on raw LUT bytes (cuda/AMsimulator.inl:13-36).
 // `wide`: 16-bit entries (carry << 15 | top 15 mantissa bits of the product), a format extension.
 __device__ __forceinline__ uint32_t am_mul_bits(uint32_t at, uint32_t bt, const uint8_t* __restrict__ lut, int m,

@@ -89,7 +89,7 @@ class _ConvamBiasActFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = ops.convam_filter_grad(w.shape, x, g, strides=strides, padding=padding, mant_mul_lut=lut, deterministic=det)
         if has_bias and ctx.needs_input_grad[2]:
-            db = g.sum((0, 1, 2))
+            db = ops.bias_grad(g)
         return dx, dw, db, None, None, None, None, None
 
 
@@ -107,7 +107,7 @@ class _DenseamBiasActFn(torch.autograd.Function):
         lut, det, has_bias = ctx.cfg
         g = (torch.ops.aten.threshold_backward(dy, y, 0.0) if y is not None else dy).contiguous()
         dx, dw = ops.denseam_grad(g, x, w, lut, deterministic=det)
-        db = g.sum(0) if has_bias and ctx.needs_input_grad[2] else None
+        db = ops.bias_grad(g) if has_bias and ctx.needs_input_grad[2] else None
         return dx, dw, db, None, None, None
 
 

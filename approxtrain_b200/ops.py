@@ -32,7 +32,7 @@ from ._lib import AmsimError, lib, check
 
 __all__ = [
     "AMLut", "get_lut", "am_multiply", "conv2d_geometry", "convam", "convam_input_grad", "convam_filter_grad",
-    "denseam", "denseam_grad", "matmulam", "convam_bias_act", "denseam_bias_act", "AmsimError",
+    "denseam", "denseam_grad", "matmulam", "convam_bias_act", "denseam_bias_act", "bias_grad", "AmsimError",
 ]
 
 
@@ -404,6 +404,26 @@ def matmulam(a: torch.Tensor, b: torch.Tensor, transpose_a: bool = False, transp
     return out
 
 
+def bias_grad(out_backprop: torch.Tensor) -> torch.Tensor:
+    """Gradient of a bias that was added along the last axis: the sum of ``out_backprop`` over all
+    other axes (TensorFlow's BiasAddGrad behind the reference's Keras layers,
+    am_convolutional.py:267-292, amdenselayer.py:222-226).  Exact FP32 adds in a fixed order, one
+    read of the gradient."""
+    g = _prep(out_backprop, "out_backprop")
+    if g.dtype != torch.float32 or g.dim() < 1:
+        raise TypeError("bias_grad takes a float32 tensor of rank >= 1")
+    cols = g.shape[-1]
+    rows = g.numel() // cols if cols else 0
+    db = torch.empty(cols, dtype=torch.float32, device=g.device)
+    if cols == 0:
+        return db
+    ws_bytes = lib.amsim_bias_grad_workspace(rows, cols)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=g.device) if ws_bytes else None
+    with torch.cuda.device(g.device):
+        check(lib.amsim_bias_grad(_stream(), _ptr(g), _ptr(db), rows, cols, _ptr(ws) if ws is not None else None, ws_bytes))
+    return db
+
+
 def _install_nvtx_ranges() -> None:
     """With AMSIM_NVTX set in the environment every op call is bracketed by an NVTX range
     named after the op and its output shape, so a timeline profiler shows the ops by name
@@ -414,7 +434,7 @@ def _install_nvtx_ranges() -> None:
         return
     g = globals()
     for name in ("am_multiply", "convam", "convam_bias_act", "denseam_bias_act", "convam_input_grad",
-                 "convam_filter_grad", "denseam", "denseam_grad", "matmulam"):
+                 "convam_filter_grad", "denseam", "denseam_grad", "matmulam", "bias_grad"):
         fn = g[name]
 
         def wrapped(*a, __fn=fn, __name=name, **k):

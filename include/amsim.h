@@ -270,6 +270,17 @@ int amsim_matmul_ex(void* stream, const amsim_lut* lut, const float* a, const fl
                     int col_b, int transpose_a, int transpose_b, const float* alpha,
                     unsigned flags);
 
+/* Bias gradient: dbias[c] = sum over rows of grad[row][c] for a row-major rows x cols gradient
+ * (NHWC output gradient: rows = batch * out_h * out_w, cols = channels; dense: rows = batch).  An
+ * exact FP32 sum in a fixed order (the same bits on every run), bound by one read of `grad`.  In
+ * the reference this is TensorFlow's stock BiasAddGrad behind the Keras layers' bias add
+ * (python/keras/layers/am_convolutional.py:267-292, amdenselayer.py:222-226), not part of its
+ * custom ops; it is here because it sits between the AM ops of every training step.
+ * `workspace`: amsim_bias_grad_workspace(rows, cols) bytes of device scratch, 16-byte aligned. */
+size_t amsim_bias_grad_workspace(long long rows, int cols);
+int amsim_bias_grad(void* stream, const float* grad, float* dbias, long long rows, int cols,
+                    void* workspace, size_t workspace_bytes);
+
 /* Number of kernels this library has launched since it was loaded (all devices, all
  * streams).  For benchmarks that report their launch count; no reference counterpart. */
 unsigned long long amsim_debug_launch_count(void);

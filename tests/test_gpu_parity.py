@@ -1061,3 +1061,20 @@ def test_reference_gemm_known_inputs(ops, oracle, luts, name):
     # the dense entry points compute the same product
     y = ops.denseam(dev(a), dev(b), lut_path(name), deterministic=True).cpu().numpy()
     assert_bit_equal(y, want, f"reference GEMM case through Denseam, {name}")
+
+
+@pytest.mark.parametrize("shape", [(32, 55, 55, 64), (8, 14, 14, 1024), (16, 28, 28, 6), (128, 10), (3, 7, 5, 2048), (1, 1000), (5, 0 + 1, 1, 3)])
+def test_bias_gradient_is_the_exact_column_sum(ops, shape):
+    """dbias[c] = sum of the output gradient over every other axis: exact FP32 adds in a fixed order.
+    Compared with a float64 sum (the FP32 result is within a few ulp of accumulated rounding) and
+    with itself (same bits on a second run, and on a copy at another address)."""
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    dy = torch.randn(*shape, device="cuda", generator=g)
+    got = ops.bias_grad(dy)
+    want = dy.double().reshape(-1, shape[-1]).sum(0)
+    scale = dy.double().abs().reshape(-1, shape[-1]).sum(0).clamp_min(1e-30)
+    assert got.shape == (shape[-1],)
+    assert float(((got.double() - want).abs() / scale).max()) <= 1e-6
+    assert torch.equal(got, ops.bias_grad(dy.clone()))
+    ints = torch.randint(-3, 4, shape, device="cuda", generator=g).float()   # small integers: every partial sum is exact
+    assert torch.equal(ops.bias_grad(ints), ints.reshape(-1, shape[-1]).sum(0))
