@@ -512,6 +512,10 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
     if (sw().balanced >= 0) mode = sw().balanced != 0 && grid >= 1;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     CUDA_TRY(cudaStreamIsCapturing(st, &cap));
+    // Inside a graph capture, launches whose tiles fill less than half of the resident slots take the
+    // cluster split below instead: it needs no counter memset node, and for launch-bound networks the
+    // replayed graph measured 2-6 % faster that way (LeNet-5 268 k -> 284 k img/s).
+    if (cap != cudaStreamCaptureStatusNone && sw().balanced < 0 && ctas * 2 <= slots && nkb >= 4) mode = 0;
     if (mode && slots > 0) {
       p.sk_iters = iters;
       p.sk_ptiles = ptiles;
@@ -1337,6 +1341,7 @@ static void bias_grad_plan(long long rows, int cols, int sms, bool vec, int* cg,
   long long want = (4ll * sms + *col_tiles - 1) / *col_tiles;
   const long long most = (rows + 63) / 64;
   if (want > most) want = most;
+  if (rows * cols <= (1ll << 16)) want = 1;  // small gradients (launch-bound networks): one kernel, no second pass
   if (want < 1) want = 1;
   *rows_per_chunk = (rows + want - 1) / want;
   *chunks = (rows + *rows_per_chunk - 1) / *rows_per_chunk;
