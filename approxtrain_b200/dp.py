@@ -46,10 +46,17 @@ class DataParallelSGD:
             self._close_bucket(cur)
         self._handles = []
         self._defer_allreduce = False   # while a step is being captured into a CUDA graph
-        if self.world > 1:
-            for bi, b in enumerate(self.buckets):
-                for p in b["params"]:
-                    p.register_post_accumulate_grad_hook(self._make_hook(bi))
+        # Gradient kernels of the AM layers write straight into the bucket memory (layers.GradSink):
+        # no per-parameter accumulate kernel, and NCCL reduces the memory the kernels wrote.
+        from .layers import GradSink
+        self._sinks = []
+        for bi, b in enumerate(self.buckets):
+            hook = self._make_hook(bi) if self.world > 1 else None
+            for p in b["params"]:
+                if self.world > 1:
+                    p.register_post_accumulate_grad_hook(hook)
+                p.amsim_grad_sink = GradSink(p.grad, hook)
+                self._sinks.append(p.amsim_grad_sink)
 
     def _close_bucket(self, params):
         n = sum(p.numel() for p in params)
@@ -72,6 +79,8 @@ class DataParallelSGD:
         for b in self.buckets:
             b["flat"].zero_()
             b["pending"] = len(b["params"])
+        for s in self._sinks:
+            s.reset()
         self._handles = []
 
     def step(self, loss_fn: Callable[[], torch.Tensor]) -> torch.Tensor:

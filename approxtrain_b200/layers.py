@@ -26,11 +26,77 @@ from torch import nn
 from . import ops
 
 
+class GradSink:
+    """Where a parameter's gradient may be written directly.  A trainer that keeps gradients in its
+    own buffers (``dp.DataParallelSGD``: views into flat all-reduce buckets) attaches one to each
+    parameter as ``param.amsim_grad_sink``; the backward of an AM layer then lets the gradient kernel
+    write straight into ``view`` (autograd's accumulate kernel is skipped) and calls ``ready(param)``
+    in place of the post-accumulate hook autograd would have fired.  Only a parameter that one
+    layer call used since the trainer's last ``reset()`` is written directly; a parameter used by
+    several calls (shared weights) has its contributions summed by autograd as usual."""
+
+    def __init__(self, view: torch.Tensor, ready=None):
+        self.view = view
+        self.ready = ready
+        self.uses = 0          # layer calls that took this parameter since reset()
+
+    def reset(self):
+        self.uses = 0
+
+    def take(self):
+        """The buffer for a direct write, or None if autograd has to sum several contributions."""
+        return self.view if self.uses == 1 else None
+
+
+def _sink_of(param):
+    s = getattr(param, "amsim_grad_sink", None)
+    if not isinstance(s, GradSink) or not param.requires_grad:
+        return None
+    s.uses += 1
+    return s
+
+
+def _deliver(sink, param):
+    if sink.ready is not None:
+        sink.ready(param)
+
+
+def _filter_grad(ctx, w, x, g, strides, padding, lut, det):
+    """ConvamFilterGrad into the parameter's sink if it has a fresh one (returns None: autograd has
+    nothing left to accumulate), else as a new tensor."""
+    buf = ctx.w_sink.take() if ctx.w_sink is not None else None
+    dw = ops.convam_filter_grad(w.shape, x, g, strides=strides, padding=padding, mant_mul_lut=lut, deterministic=det, out=buf)
+    if buf is None:
+        return dw
+    _deliver(ctx.w_sink, ctx.w_param)
+    return None
+
+
+def _dense_grads(ctx, g, x, w, lut, det):
+    """DenseamGrad; the weight gradient goes into the parameter's sink if it has a fresh one."""
+    buf = ctx.w_sink.take() if (ctx.w_sink is not None and ctx.needs_input_grad[1]) else None
+    dx, dw = ops.denseam_grad(g, x, w, lut, deterministic=det, out_weights=buf)
+    if buf is None:
+        return dx, dw
+    _deliver(ctx.w_sink, ctx.w_param)
+    return dx, None
+
+
+def _bias_grad(ctx, g):
+    buf = ctx.b_sink.take() if ctx.b_sink is not None else None
+    db = ops.bias_grad(g, out=buf)
+    if buf is None:
+        return db
+    _deliver(ctx.b_sink, ctx.b_param)
+    return None
+
+
 class _ConvamFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, strides, padding, lut, deterministic):
         ctx.save_for_backward(x, w)
         ctx.cfg = (strides, padding, lut, deterministic)
+        ctx.w_param, ctx.w_sink = w, _sink_of(w)
         return ops.convam(x, w, strides=strides, padding=padding, mant_mul_lut=lut, deterministic=deterministic)
 
     @staticmethod
@@ -43,8 +109,7 @@ class _ConvamFn(torch.autograd.Function):
             dx = ops.convam_input_grad(x.shape, w, dy, strides=strides, padding=padding, mant_mul_lut=lut,
                                        deterministic=det)
         if ctx.needs_input_grad[1]:
-            dw = ops.convam_filter_grad(w.shape, x, dy, strides=strides, padding=padding, mant_mul_lut=lut,
-                                        deterministic=det)
+            dw = _filter_grad(ctx, w, x, dy, strides, padding, lut, det)
         return dx, dw, None, None, None, None
 
 
@@ -53,13 +118,14 @@ class _DenseamFn(torch.autograd.Function):
     def forward(ctx, x, w, lut, deterministic):
         ctx.save_for_backward(x, w)
         ctx.cfg = (lut, deterministic)
+        ctx.w_param, ctx.w_sink = w, _sink_of(w)
         return ops.denseam(x, w, lut, deterministic=deterministic)
 
     @staticmethod
     def backward(ctx, g):
         x, w = ctx.saved_tensors
         lut, det = ctx.cfg
-        dx, dw = ops.denseam_grad(g.contiguous(), x, w, lut, deterministic=det)
+        dx, dw = _dense_grads(ctx, g.contiguous(), x, w, lut, det)
         return dx, dw, None, None
 
 
@@ -74,6 +140,8 @@ class _ConvamBiasActFn(torch.autograd.Function):
                                 deterministic=deterministic)
         ctx.save_for_backward(x, w, y if activation == "relu" else None)
         ctx.cfg = (strides, padding, lut, deterministic, b is not None)
+        ctx.w_param, ctx.w_sink = w, _sink_of(w)
+        ctx.b_param, ctx.b_sink = b, (_sink_of(b) if b is not None else None)
         return y
 
     @staticmethod
@@ -87,9 +155,9 @@ class _ConvamBiasActFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = ops.convam_input_grad(x.shape, w, g, strides=strides, padding=padding, mant_mul_lut=lut, deterministic=det)
         if ctx.needs_input_grad[1]:
-            dw = ops.convam_filter_grad(w.shape, x, g, strides=strides, padding=padding, mant_mul_lut=lut, deterministic=det)
+            dw = _filter_grad(ctx, w, x, g, strides, padding, lut, det)
         if has_bias and ctx.needs_input_grad[2]:
-            db = ops.bias_grad(g)
+            db = _bias_grad(ctx, g)
         return dx, dw, db, None, None, None, None, None
 
 
@@ -99,6 +167,8 @@ class _DenseamBiasActFn(torch.autograd.Function):
         y = ops.denseam_bias_act(x, w, b, activation=activation, mant_mul_lut=lut, deterministic=deterministic)
         ctx.save_for_backward(x, w, y if activation == "relu" else None)
         ctx.cfg = (lut, deterministic, b is not None)
+        ctx.w_param, ctx.w_sink = w, _sink_of(w)
+        ctx.b_param, ctx.b_sink = b, (_sink_of(b) if b is not None else None)
         return y
 
     @staticmethod
@@ -106,8 +176,8 @@ class _DenseamBiasActFn(torch.autograd.Function):
         x, w, y = ctx.saved_tensors
         lut, det, has_bias = ctx.cfg
         g = (torch.ops.aten.threshold_backward(dy, y, 0.0) if y is not None else dy).contiguous()
-        dx, dw = ops.denseam_grad(g, x, w, lut, deterministic=det)
-        db = ops.bias_grad(g) if has_bias and ctx.needs_input_grad[2] else None
+        dx, dw = _dense_grads(ctx, g, x, w, lut, det)
+        db = _bias_grad(ctx, g) if has_bias and ctx.needs_input_grad[2] else None
         return dx, dw, db, None, None, None
 
 

@@ -293,9 +293,19 @@ def convam_input_grad(input_sizes: Sequence[int], filter: torch.Tensor, out_back
     return dx
 
 
+def _out_tensor(out, shape, dtype, device, name):
+    """``out=``: a caller-owned result buffer (e.g. a view into a gradient bucket); must match exactly."""
+    if out is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    if tuple(out.shape) != tuple(shape) or out.dtype != dtype or out.device != device or not out.is_contiguous():
+        raise ValueError(f"{name}: out must be a contiguous {dtype} tensor of shape {list(shape)} on {device}")
+    return out
+
+
 def convam_filter_grad(filter_sizes: Sequence[int], input: torch.Tensor, out_backprop: torch.Tensor, strides=None,
                        padding="VALID", data_format="NHWC", dilations=None, mant_mul_lut: str = "",
-                       deterministic: bool = False) -> torch.Tensor:
+                       deterministic: bool = False, out: torch.Tensor = None) -> torch.Tensor:
+    """``out`` (optional): write the gradient into this tensor instead of a new one."""
     _check_format(data_format, dilations)
     x, dy = _prep(input, "input"), _prep(out_backprop, "out_backprop")
     sizes = [int(v) for v in filter_sizes]
@@ -308,7 +318,7 @@ def convam_filter_grad(filter_sizes: Sequence[int], input: torch.Tensor, out_bac
     if tuple(dy.shape) != (n, oh, ow, k) or ci != c:
         raise ValueError(f"out_backprop shape {list(dy.shape)} does not match the forward output {[n, oh, ow, k]}")
     lut = get_lut(mant_mul_lut, x.device)
-    dw = torch.empty((kh, kw, c, k), dtype=x.dtype, device=x.device)
+    dw = _out_tensor(out, (kh, kw, c, k), x.dtype, x.device, "convam_filter_grad")
     if dw.numel() == 0:
         return dw
     fl = _flags(deterministic) | _dtype_flag(x, dy)
@@ -338,8 +348,9 @@ def denseam(input: torch.Tensor, weights: torch.Tensor, mant_mul_lut: str = "",
 
 
 def denseam_grad(grad: torch.Tensor, input: torch.Tensor, weights: torch.Tensor, mant_mul_lut: str = "",
-                 deterministic: bool = False):
-    """Returns (grad_input, grad_weights) like DenseamGrad (denseam.cc:177-235)."""
+                 deterministic: bool = False, out_weights: torch.Tensor = None):
+    """Returns (grad_input, grad_weights) like DenseamGrad (denseam.cc:177-235).  ``out_weights``
+    (optional): write grad_weights into this tensor instead of a new one."""
     g, x, w = _prep(grad, "grad"), _prep(input, "input"), _prep(weights, "weights")
     b, kin = x.shape
     u = w.shape[1]
@@ -348,7 +359,7 @@ def denseam_grad(grad: torch.Tensor, input: torch.Tensor, weights: torch.Tensor,
     lut = get_lut(mant_mul_lut, x.device)
     fl = _flags(deterministic) | _dtype_flag(g, x, w)
     dx = torch.empty_like(x)
-    dw = torch.empty_like(w)
+    dw = _out_tensor(out_weights, tuple(w.shape), w.dtype, w.device, "denseam_grad")
     ws_bytes = lib.amsim_dense_bwd_weight_workspace(b, u, kin, fl)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
     with torch.cuda.device(x.device):
@@ -404,17 +415,17 @@ def matmulam(a: torch.Tensor, b: torch.Tensor, transpose_a: bool = False, transp
     return out
 
 
-def bias_grad(out_backprop: torch.Tensor) -> torch.Tensor:
+def bias_grad(out_backprop: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
     """Gradient of a bias that was added along the last axis: the sum of ``out_backprop`` over all
     other axes (TensorFlow's BiasAddGrad behind the reference's Keras layers,
     am_convolutional.py:267-292, amdenselayer.py:222-226).  Exact FP32 adds in a fixed order, one
-    read of the gradient."""
+    read of the gradient.  ``out`` (optional): write the result into this tensor."""
     g = _prep(out_backprop, "out_backprop")
     if g.dtype != torch.float32 or g.dim() < 1:
         raise TypeError("bias_grad takes a float32 tensor of rank >= 1")
     cols = g.shape[-1]
     rows = g.numel() // cols if cols else 0
-    db = torch.empty(cols, dtype=torch.float32, device=g.device)
+    db = _out_tensor(out, (cols,), torch.float32, g.device, "bias_grad")
     if cols == 0:
         return db
     ws_bytes = lib.amsim_bias_grad_workspace(rows, cols)

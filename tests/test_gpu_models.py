@@ -220,3 +220,47 @@ def test_cuda_graph_replay_matches_eager_steps():
     eager = run(False)
     graph = run(True)
     assert graph == eager[3:], (graph, eager)
+
+
+def test_gradients_written_straight_into_the_buckets_equal_autograd_accumulation():
+    """DataParallelSGD hands every parameter a view into its flat gradient bucket; the AM layers'
+    gradient kernels (filter / weight gradient, bias gradient) write into that view directly.  The
+    result must be the bits autograd's own accumulation gives (sinks removed), also for a layer
+    that is applied twice in one step (shared weights: autograd sums the two contributions)."""
+    from approxtrain_b200.layers import AMConv2D, denseam
+    from approxtrain_b200.dp import DataParallelSGD
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            kw = dict(mant_mul_lut=lut_path("MBM_7"), kernel_initializer="he_normal")
+            self.c1 = AMConv2D(4, 8, 3, padding="same", activation="relu", **kw)
+            self.c2 = AMConv2D(8, 8, 3, padding="same", activation="relu", **kw)   # applied twice
+            self.f = denseam(8 * 6 * 6, 10, **kw)
+
+        def forward(self, x):
+            y = self.c2(self.c2(self.c1(x)))
+            return self.f(y.reshape(y.shape[0], -1))
+
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(16, 6, 6, 4, generator=g).cuda()
+    y = torch.randint(0, 10, (16,), generator=g).cuda()
+
+    def run(direct):
+        torch.manual_seed(2)
+        net = Net().cuda()
+        tr = DataParallelSGD(net, lr=0.05)
+        if not direct:
+            for p in net.parameters():
+                del p.amsim_grad_sink
+            tr._sinks = []
+        losses = [float(tr.step(lambda: torch.nn.functional.cross_entropy(net(x), y))) for _ in range(3)]
+        used = [s.uses for s in tr._sinks]
+        return losses, [p.detach().clone() for p in net.parameters()], used
+
+    l_direct, p_direct, used = run(True)
+    l_plain, p_plain, _ = run(False)
+    assert sorted(used) == [1, 1, 1, 1, 2, 2]     # c1 and f (weight, bias) once each, c2 twice
+    assert l_direct == l_plain
+    for a, b in zip(p_direct, p_plain):
+        assert torch.equal(a, b)
