@@ -264,3 +264,25 @@ def test_gradients_written_straight_into_the_buckets_equal_autograd_accumulation
     assert l_direct == l_plain
     for a, b in zip(p_direct, p_plain):
         assert torch.equal(a, b)
+
+
+def test_bench_prints_one_complete_line_for_a_small_workload():
+    """bench.py end to end on the smallest train workload: timed region, end-to-end leg, the
+    instrumented step behind `am_ops` (event pairs around every op call, including the ones that
+    write into gradient buckets), CUDA-graph replay, one JSON line with the keys the contract names."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--workload", "lenet5", "--steps", "5", "--warmup", "3",
+                          "--no-cpu-baseline"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-3000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "dtype",
+                "data", "config", "clocks", "e2e", "gpu_launches", "roofline", "am_ops"):
+        assert key in d, key
+    assert d["value"] > 0 and d["gpu_launches"] > 0 and d["e2e"]["value"] > 0 and d["e2e"]["h2d_bytes_per_step"] > 0
+    assert d["am_ops"]["layers"] and d["roofline"]["frac"] > 0
