@@ -714,8 +714,9 @@ int launch_wide_fgrad_t(cudaStream_t st, Params& p, int device) {
   CUDA_TRY(cudaGetLastError());
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
+    const int lanes = reduce_lanes(p.splits);
     AMSIM_COUNT_LAUNCH();
-    reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq);
+    reduce_splits<<<reduce_blocks(n, lanes), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq, lanes);
     CUDA_TRY(cudaGetLastError());
   }
   return AMSIM_OK;
@@ -733,8 +734,9 @@ int launch_fgrad_t(cudaStream_t st, const Params& p, int device) {
   CUDA_TRY(cudaGetLastError());
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
+    const int lanes = reduce_lanes(p.splits);
     AMSIM_COUNT_LAUNCH();
-    reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq);
+    reduce_splits<<<reduce_blocks(n, lanes), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq, lanes);
     CUDA_TRY(cudaGetLastError());
   }
   return AMSIM_OK;
@@ -752,8 +754,9 @@ int launch_fgrad_thin_t(cudaStream_t st, Params& p, int device) {
   CUDA_TRY(cudaGetLastError());
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
+    const int lanes = reduce_lanes(p.splits);
     AMSIM_COUNT_LAUNCH();
-    reduce_splits<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq);
+    reduce_splits<<<reduce_blocks(n, lanes), 256, 0, st>>>(p.ws, p.O, n, p.splits, p.Q, p.o_sp, p.o_sq, lanes);
     CUDA_TRY(cudaGetLastError());
   }
   return AMSIM_OK;
@@ -1386,7 +1389,8 @@ int amsim_bias_grad(void* stream, const float* grad, float* dbias, long long row
   CUDA_TRY(cudaGetLastError());
   if (chunks > 1) {
     AMSIM_COUNT_LAUNCH();
-    reduce_splits<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(part, dbias, cols, (int)chunks, cols, 0, 1);
+    const int lanes = reduce_lanes((int)chunks);
+    reduce_splits<<<reduce_blocks(cols, lanes), 256, 0, st>>>(part, dbias, cols, (int)chunks, cols, 0, 1, lanes);
     CUDA_TRY(cudaGetLastError());
   }
   return AMSIM_OK;
