@@ -453,7 +453,10 @@ cudaError_t balanced_scratch_release(cudaStream_t st, const BalancedScratch& b) 
 // shared memory it is about 3 % slower per padded product (8 instead of 12 warps per
 // multiprocessor hide less lookup latency) and only pays where its 288-row tiles remove padding
 // (576 rows: 1.40 -> 1.30 ms); with an additive table (no lookups, issue bound) it is 20-28 % faster.
-constexpr double kWideRateTable = 1.03, kWideRateAdditive = 0.80;
+// The 288-row tile, whose lookups take the table row from a uniform register, is 2 % faster than
+// fgrad_gemm when its CTAs fill the device (3x3x256x256: 1.278 -> 1.252 ms) and slower when they
+// do not (3x3x512x512, 256 CTAs on 296 slots: +5.6 %).
+constexpr double kWideRateTable = 1.03, kWideRateTable9Full = 0.98, kWideRateAdditive = 0.80;
 
 template <bool EXACT, bool VEC, int LM>
 int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
@@ -628,15 +631,20 @@ struct FgradPlan {
 // kernel (128-bit gathers; `additive`: the table is additive, else it sits in shared memory): the
 // tile height with the least padded work, weighted by the kernels' measured rates.  0 = the
 // 128-row kernel.
+FgradPlan plan_fgrad(int P, int Q, int K, bool exact, int np, int sms);
+
 int pick_fgrad_rows(int P, int Q, int K, int sms, bool additive) {
   if (sw().wide == 0) return 0;
   auto padded = [&](int bp) { return (double)(((long long)P + bp - 1) / bp) * bp; };
   int best = 8;
   double cost = padded(256);
-  if (padded(288) < cost) { best = 9; cost = padded(288); }
+  if (padded(288) <= cost) { best = 9; cost = padded(288); }
   if (sw().wide > 0) return best;
-  if (cost * (additive ? kWideRateAdditive : kWideRateTable) >= padded(128)) return 0;
   const long long tiles = (((long long)P + 32 * best - 1) / (32 * best)) * (((long long)Q + BQ - 1) / BQ);
+  double rate = additive ? kWideRateAdditive : kWideRateTable;
+  if (!additive && best == 9 && (double)tiles * plan_fgrad(P, Q, K, false, 9, sms).splits >= 0.95 * 2 * sms)
+    rate = kWideRateTable9Full;
+  if (cost * rate >= padded(128)) return 0;
   if (tiles * (((long long)K + BK - 1) / BK) < 8ll * 2 * sms) return 0;  // too small to fill the device a few times over
   return best;
 }
