@@ -560,13 +560,22 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   const float* __restrict__ Ug = prm.U + (long long)tile_z * prm.u_bs;
   float* __restrict__ Og = prm.O + (long long)tile_z * prm.o_bs;
 
-  // ---- this thread's share of the V tile: 2 rows (p) x 2 groups of 4 k ------
-  int pl[2], r0[2], c0[2];
-  long long nb[2];
-  bool pv[2];
+  // ---- this thread's share of the V tile: 4 rows (p) x one group of 4 k ------
+  // A warp's 128-bit gather covers 8 rows x 64 contiguous bytes (the four k groups of a stage):
+  // half as many cache lines per request as 16 rows x 32 bytes.  The L1 data stage spends its
+  // cycles per line touched, and shares them with the table lookups: with 16 lines per request
+  // the gathers took a tenth of the data pipe (24 cycles per request, where the filter
+  // gradient's contiguous requests take 5); this layout made the 3x3 forward and input-gradient
+  // kernels 3-5 % faster.  In shared memory the rows of k groups 2 and 3 are stored with
+  // bit 3 of the column flipped, so that the four groups' stores fall into different banks;
+  // the inner loop reads k rows 8..15 at its own column with the same bit flipped.
+  constexpr int NPX = 4;
+  int pl[NPX], r0[NPX], c0[NPX];
+  long long nb[NPX];
+  bool pv[NPX];
 #pragma unroll
-  for (int ip = 0; ip < 2; ++ip) {
-    pl[ip] = (ip * 4 * WP + w) * 16 + (lane & 15);
+  for (int ip = 0; ip < NPX; ++ip) {
+    pl[ip] = (ip * 4 * WP + w) * 8 + (lane >> 2);
     const uint32_t pg = (uint32_t)(p0 + pl[ip]);
     pv[ip] = pg < (uint32_t)prm.P;
     const uint32_t n = fdiv(pg, g.d_img);
@@ -577,23 +586,22 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
     c0[ip] = (int)b * g.ps_w - g.off_l;
     nb[ip] = (long long)n * ((long long)g.SH * g.SW * g.SC);
   }
-  const int kg_sub = lane >> 4;
+  const int kg = lane & 3;  // this thread's group of four reduction steps of a stage
 
-  float4 vraw[2][2];  // [k group][row]
+  float4 vraw[NPX];
   float uraw[NU];
   const bool u_kmajor = prm.u_sk == 1 && prm.u_sq != 1;
 
   auto load_tile = [&](int kb) {
-#pragma unroll
-    for (int ik = 0; ik < 2; ++ik) {
-      const int kglob = kb * BK + 4 * (2 * ik + kg_sub);
+    {
+      const int kglob = kb * BK + 4 * kg;
       if (VEC) {
         const uint32_t tap = fdiv((uint32_t)kglob, g.d_sc);
         const int ch = kglob - (int)tap * g.SC;
         const int kh = (int)fdiv(tap, g.d_kw);
         const int kw = (int)tap - kh * g.KW;
 #pragma unroll
-        for (int ip = 0; ip < 2; ++ip) {
+        for (int ip = 0; ip < NPX; ++ip) {
           float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
           const int u = r0[ip] + kh, v = c0[ip] + kw;
           if (pv[ip] && kglob < prm.K && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w) {
@@ -604,10 +612,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
             if ((!EXACT || (row * g.dil_h == u && col * g.dil_w == v)) && AMSIM_IN(prm, BUF_V, src, float4))
               val = __ldg(reinterpret_cast<const float4*>(src));
           }
-          vraw[ik][ip] = val;
+          vraw[ip] = val;
         }
       } else {
-        float tmp[2][4];
+        float tmp[NPX][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int kj = kglob + j;
@@ -616,7 +624,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
           const int kh = (int)fdiv(tap, g.d_kw);
           const int kw = (int)tap - kh * g.KW;
 #pragma unroll
-          for (int ip = 0; ip < 2; ++ip) {
+          for (int ip = 0; ip < NPX; ++ip) {
             float val = 0.f;
             const int u = r0[ip] + kh, v = c0[ip] + kw;
             if (prm.v_trans) {
@@ -631,7 +639,7 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
           }
         }
 #pragma unroll
-        for (int ip = 0; ip < 2; ++ip) vraw[ik][ip] = make_float4(tmp[ip][0], tmp[ip][1], tmp[ip][2], tmp[ip][3]);
+        for (int ip = 0; ip < NPX; ++ip) vraw[ip] = make_float4(tmp[ip][0], tmp[ip][1], tmp[ip][2], tmp[ip][3]);
       }
     }
     if (prm.u_vec) {
@@ -679,16 +687,16 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   auto store_tile = [&](int buf) {
     uint32_t* vs = Vs + buf * BK * VS;
     uint32_t hz = 0;
+    {
+      const int krow = 4 * kg, flip = (kg >> 1) << 3;
 #pragma unroll
-    for (int ik = 0; ik < 2; ++ik) {
-      const int krow = 4 * (2 * ik + kg_sub);
-#pragma unroll
-      for (int ip = 0; ip < 2; ++ip) {
-        const float4 f = vraw[ik][ip];
-        vs[(krow + 0) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.x), prm.m);
-        vs[(krow + 1) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.y), prm.m);
-        vs[(krow + 2) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.z), prm.m);
-        vs[(krow + 3) * VS + pl[ip]] = enc_v<EXACT, LM>(__float_as_uint(f.w), prm.m);
+      for (int ip = 0; ip < NPX; ++ip) {
+        const float4 f = vraw[ip];
+        const int col = pl[ip] ^ flip;
+        vs[(krow + 0) * VS + col] = enc_v<EXACT, LM>(__float_as_uint(f.x), prm.m);
+        vs[(krow + 1) * VS + col] = enc_v<EXACT, LM>(__float_as_uint(f.y), prm.m);
+        vs[(krow + 2) * VS + col] = enc_v<EXACT, LM>(__float_as_uint(f.z), prm.m);
+        vs[(krow + 3) * VS + col] = enc_v<EXACT, LM>(__float_as_uint(f.w), prm.m);
         if (HAZARD_CHECK)
           hz |= hazard_bits(__float_as_uint(f.x), false) | hazard_bits(__float_as_uint(f.y), false) |
                 hazard_bits(__float_as_uint(f.z), false) | hazard_bits(__float_as_uint(f.w), false);
@@ -744,36 +752,39 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   for (int kb = kb_begin; kb < nkb; ++kb) {
     const int buf = (kb - kb_begin) & 1;
     if (kb + 1 < nkb) load_tile(kb + 1);
-    const uint32_t* vs = Vs + buf * BK * VS + vcol;
+    const uint32_t* vs = Vs + buf * BK * VS;
     const uint32_t* us = Us + buf * BK * US + ucol;
+    // k rows 8..15 sit at the column with bit 3 flipped (see the staging above)
+#define AMSIM_K_HALVES(...)                                                   \
+  _Pragma("unroll 1") for (int kh = 0; kh < BK; kh += 8) {                     \
+    const uint32_t* vh = vs + kh * VS + (vcol ^ kh);                           \
+    const uint32_t* uh = us + kh * US;                                         \
+    AMSIM_UNROLL_K                                                             \
+    for (int kk = 0; kk < 8; ++kk)                                             \
+      mac_step<__VA_ARGS__>(acc, vh + kk * VS, uh + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj, \
+                            prm.lut_raw);                                      \
+  }
+    static_assert(BK == 16, "two halves of eight reduction steps");
     if (HAZARD_CHECK) {
       uint32_t hz = 0;
 #pragma unroll
       for (int i = 0; i < 4 * WP; ++i) hz |= Fs[buf * 4 * WP + i];
       if (hazard_free(hz) && !prm.exact_only) {
-AMSIM_UNROLL_K
-        for (int kk = 0; kk < BK; ++kk)
-          mac_step<false, LM, true>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask,
-                                    prm.cadj, prm.lut_raw);
+        AMSIM_K_HALVES(false, LM, true)
       } else {
-AMSIM_UNROLL_K
-        for (int kk = 0; kk < BK; ++kk)
-          mac_step<true, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
-                             prm.lut_raw);
+        AMSIM_K_HALVES(true, LM)
       }
     } else if (QS > 1) {
 AMSIM_UNROLL_K
       for (int kq = 0; kq < BK / QS; ++kq) {
         const int kk = kq * QS + ksub;
-        mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
-                            prm.lut_raw);
+        mac_step<EXACT, LM>(acc, vs + kk * VS + (vcol ^ (kk & 8)), us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask,
+                            prm.cadj, prm.lut_raw);
       }
     } else {
-AMSIM_UNROLL_K
-      for (int kk = 0; kk < BK; ++kk)
-        mac_step<EXACT, LM>(acc, vs + kk * VS, us + kk * US, lut_base, prm.rmask, prm.mult, prm.cmask, prm.cadj,
-                            prm.lut_raw);
+      AMSIM_K_HALVES(EXACT, LM)
     }
+#undef AMSIM_K_HALVES
     if (kb + 1 < nkb) store_tile(buf ^ 1);
     __syncthreads();
   }
