@@ -67,6 +67,7 @@ struct Switches {
   int exact_only = 0;       // AMSIM_EXACT_ONLY=1        deterministic kernels never use the fast arithmetic
   int no_additive = 0;      // AMSIM_NO_ADDITIVE=1       additive tables are looked up like any other (at lut_open)
   int wide = -1;            // AMSIM_WIDE=0/1            wide-tile filter gradient: never / whenever eligible
+  int capture_cluster = -1; // AMSIM_CAPTURE_CLUSTER=0/1 small launches inside a graph capture: balanced / cluster split
   int bounds_shrink = 0;    // AMSIM_BOUNDS_SHRINK=n     bounds-checking build only: the output's recorded extent is n bytes
                             //                           short, so its last stores are caught (self-test of the checker)
 };
@@ -92,6 +93,7 @@ void load_switches() {
   flag("AMSIM_EXACT_ONLY", w.exact_only);
   flag("AMSIM_NO_ADDITIVE", w.no_additive);
   tri("AMSIM_WIDE", w.wide);
+  tri("AMSIM_CAPTURE_CLUSTER", w.capture_cluster);
   tri("AMSIM_BOUNDS_SHRINK", w.bounds_shrink);
   g_sw = w;
 }
@@ -410,6 +412,11 @@ struct BalancedScratch {
   float* ws = nullptr;
   bool pooled = false;
 };
+// The persistent buffer starts with room for the per-tile counters of a launch.  They are zeroed when
+// the buffer is created and the CTA that completes a tile puts its counter back to zero, so launches
+// inside a captured graph need no memset node.
+constexpr size_t kPersistentCounters = 1u << 16;
+constexpr size_t kPersistentCounterBytes = kPersistentCounters * sizeof(int);
 
 int balanced_scratch_acquire(cudaStream_t st, int device, size_t bytes, bool capturing, BalancedScratch* out) {
   static std::mutex mu;
@@ -425,7 +432,7 @@ int balanced_scratch_acquire(cudaStream_t st, int device, size_t bytes, bool cap
     }
     if (slot.second < bytes) {
       void* fresh = nullptr;
-      if (cudaMalloc(&fresh, bytes) == cudaSuccess) {
+      if (cudaMalloc(&fresh, bytes) == cudaSuccess && cudaMemset(fresh, 0, kPersistentCounterBytes) == cudaSuccess) {
         // the old buffer may still be referenced by instantiated graphs: it is kept, not freed
         slot.first = fresh;
         slot.second = bytes;
@@ -511,29 +518,40 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
     if (iters / grid < 2) grid = iters / 2;
     // measured: pays when the plain grid is at most two waves with a last wave under ~93 % full
     // (one wave at 88 %: -7 %); with more waves the plain grid's tail is already short
-    int mode = waves <= 2 && fill < 0.93 && grid >= 2 && nkb >= 2;
+    // with long reductions (shape A of the 3x3 microbenchmark: 3.5 waves of 36 blocks) it also pays on
+    // larger grids (-2.5 %); with short ones (1x1 layers of 4-8 blocks) the parked partial tiles cost
+    // more than the tail (+3-4 %)
+    int mode = ((waves <= 2 && fill < 0.93) || (nkb >= 16 && fill < 0.95)) && grid >= 2 && nkb >= 2;
     if (sw().balanced >= 0) mode = sw().balanced != 0 && grid >= 1;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     CUDA_TRY(cudaStreamIsCapturing(st, &cap));
-    // Inside a graph capture, launches whose tiles fill less than half of the resident slots take the
-    // cluster split below instead: it needs no counter memset node, and for launch-bound networks the
-    // replayed graph measured 2-6 % faster that way (LeNet-5 268 k -> 284 k img/s).
-    if (cap != cudaStreamCaptureStatusNone && sw().balanced < 0 && ctas * 2 <= slots && nkb >= 4) mode = 0;
+    // Inside a graph capture the tiniest launches (LeNet-5's dense layers: two tiles of 8-16 reduction
+    // blocks) take the cluster split below instead, which adds partial tiles through distributed
+    // shared memory rather than through parked tiles in global memory: the replayed LeNet-5 step
+    // measured 4 % faster that way; anything larger is faster balanced (ResNet-50 +2 %,
+    // LeNet-300-100 +3 %; the persistent scratch needs no memset node).
+    const bool capturing = cap != cudaStreamCaptureStatusNone;
+    bool tiny = ctas * 2 <= slots && nkb >= 4 && iters <= 64;
+    if (sw().capture_cluster >= 0) tiny = sw().capture_cluster != 0 && ctas * 2 <= slots && nkb >= 4;
+    if (capturing && sw().balanced < 0 && tiny) mode = 0;
     if (mode && slots > 0) {
       p.sk_iters = iters;
       p.sk_ptiles = ptiles;
       p.sk_qtiles = qtiles;
       p.sk_grid = (int)grid;
       const size_t slot_bytes = (size_t)grid * 2 * TR * TC * L::NT * sizeof(float);
-      const size_t bytes = slot_bytes + (size_t)ctas * sizeof(int);
+      // [counters kept at zero between launches][parked tiles][counters of a launch with more tiles than that]
+      const size_t bytes = kPersistentCounterBytes + slot_bytes + (size_t)ctas * sizeof(int);
       BalancedScratch sc;
-      rc = balanced_scratch_acquire(st, device, bytes, cap != cudaStreamCaptureStatusNone, &sc);
+      rc = balanced_scratch_acquire(st, device, bytes, capturing, &sc);
       if (rc) return rc;
       if (sc.ws) {
-        p.ws = sc.ws;
-        p.sk_count = reinterpret_cast<int*>(reinterpret_cast<char*>(p.ws) + slot_bytes);
-        fill_bounds(p, device, p.ws, bytes);
-        cudaError_t e1 = cudaMemsetAsync(p.sk_count, 0, (size_t)ctas * sizeof(int), st);
+        char* base = reinterpret_cast<char*>(sc.ws);
+        p.ws = reinterpret_cast<float*>(base + kPersistentCounterBytes);
+        const bool clean = !sc.pooled && (size_t)ctas <= kPersistentCounters;  // persistent buffer: zero already
+        p.sk_count = reinterpret_cast<int*>(clean ? base : base + kPersistentCounterBytes + slot_bytes);
+        fill_bounds(p, device, base, bytes);
+        cudaError_t e1 = clean ? cudaSuccess : cudaMemsetAsync(p.sk_count, 0, (size_t)ctas * sizeof(int), st);
         if (e1 == cudaSuccess) {
           AMSIM_COUNT_LAUNCH();
           gather_gemm<1, EXACT, VEC, GM_BALANCED, LM><<<dim3((unsigned)grid), L::NT, smem_plain, st>>>(p);

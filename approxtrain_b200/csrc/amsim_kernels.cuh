@@ -536,30 +536,21 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
     run_end = balanced_begin((long long)blockIdx.x + 1, prm.sk_iters, prm.sk_grid);
     if (run_at >= run_end) return;
   }
-  do {
-  int tile_p, tile_q, tile_z, kb_begin, nkb;
-  if (BALANCED) {
-    const long long tile = run_at / nkb_all;
-    kb_begin = (int)(run_at - tile * nkb_all);
-    nkb = kb_begin + (int)min((long long)(nkb_all - kb_begin), run_end - run_at);
-    run_at += nkb - kb_begin;
-    tile_q = (int)(tile % prm.sk_qtiles);
+  // ---- the segment being staged: a tile and a range of its reduction blocks ----------------
+  // (in balanced mode the staging moves on to the next segment during the last stage of the
+  // current one, so these are variables; the tile being accumulated is kept in seg_at)
+  int tile_p = 0, tile_q = 0, tile_z = 0, kb_begin = 0, nkb = 0, p0 = 0, q0 = 0;
+  const float* __restrict__ Vg = prm.V;
+  const float* __restrict__ Ug = prm.U;
+  auto decode_tile = [&](long long at, int& tp, int& tq, int& tz, int& kb0, int& kb1) {
+    const long long tile = at / nkb_all;
+    kb0 = (int)(at - tile * nkb_all);
+    kb1 = kb0 + (int)min((long long)(nkb_all - kb0), run_end - at);
+    tq = (int)(tile % prm.sk_qtiles);
     const long long rest = tile / prm.sk_qtiles;
-    tile_p = (int)(rest % prm.sk_ptiles);
-    tile_z = (int)(rest / prm.sk_ptiles);
-  } else {
-    tile_p = blockIdx.x / ksplit;
-    tile_q = blockIdx.y;
-    tile_z = blockIdx.z;
-    const int per = (nkb_all + ksplit - 1) / ksplit;
-    kb_begin = krank * per;
-    nkb = min(kb_begin + per, nkb_all);
-  }
-  const int p0 = tile_p * BP, q0 = tile_q * BQE;
-  const float* __restrict__ Vg = prm.V + (long long)tile_z * prm.v_bs;
-  const float* __restrict__ Ug = prm.U + (long long)tile_z * prm.u_bs;
-  float* __restrict__ Og = prm.O + (long long)tile_z * prm.o_bs;
-
+    tp = (int)(rest % prm.sk_ptiles);
+    tz = (int)(rest / prm.sk_ptiles);
+  };
   // ---- this thread's share of the V tile: 4 rows (p) x one group of 4 k ------
   // A warp's 128-bit gather covers 8 rows x 64 contiguous bytes (the four k groups of a stage):
   // half as many cache lines per request as 16 rows x 32 bytes.  The L1 data stage spends its
@@ -574,18 +565,38 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   long long nb[NPX];
   bool pv[NPX];
 #pragma unroll
-  for (int ip = 0; ip < NPX; ++ip) {
-    pl[ip] = (ip * 4 * WP + w) * 8 + (lane >> 2);
-    const uint32_t pg = (uint32_t)(p0 + pl[ip]);
-    pv[ip] = pg < (uint32_t)prm.P;
-    const uint32_t n = fdiv(pg, g.d_img);
-    const uint32_t rem = pg - n * (uint32_t)(g.PH * g.PW);
-    const uint32_t a = fdiv(rem, g.d_pw);
-    const uint32_t b = rem - a * (uint32_t)g.PW;
-    r0[ip] = (int)a * g.ps_h - g.off_t;
-    c0[ip] = (int)b * g.ps_w - g.off_l;
-    nb[ip] = (long long)n * ((long long)g.SH * g.SW * g.SC);
-  }
+  for (int ip = 0; ip < NPX; ++ip) pl[ip] = (ip * 4 * WP + w) * 8 + (lane >> 2);
+  // Points the staging at the segment that starts at run position run_at (balanced mode; advances
+  // run_at past it) or at this CTA's tile (plain and cluster launches).
+  auto next_segment = [&]() {
+    if (BALANCED) {
+      decode_tile(run_at, tile_p, tile_q, tile_z, kb_begin, nkb);
+      run_at += nkb - kb_begin;
+    } else {
+      tile_p = blockIdx.x / ksplit;
+      tile_q = blockIdx.y;
+      tile_z = blockIdx.z;
+      const int per = (nkb_all + ksplit - 1) / ksplit;
+      kb_begin = krank * per;
+      nkb = min(kb_begin + per, nkb_all);
+    }
+    p0 = tile_p * BP;
+    q0 = tile_q * BQE;
+    Vg = prm.V + (long long)tile_z * prm.v_bs;
+    Ug = prm.U + (long long)tile_z * prm.u_bs;
+#pragma unroll
+    for (int ip = 0; ip < NPX; ++ip) {
+      const uint32_t pg = (uint32_t)(p0 + pl[ip]);
+      pv[ip] = pg < (uint32_t)prm.P;
+      const uint32_t n = fdiv(pg, g.d_img);
+      const uint32_t rem = pg - n * (uint32_t)(g.PH * g.PW);
+      const uint32_t a = fdiv(rem, g.d_pw);
+      const uint32_t b = rem - a * (uint32_t)g.PW;
+      r0[ip] = (int)a * g.ps_h - g.off_t;
+      c0[ip] = (int)b * g.ps_w - g.off_l;
+      nb[ip] = (long long)n * ((long long)g.SH * g.SW * g.SC);
+    }
+  };
   const int kg = lane & 3;  // this thread's group of four reduction steps of a stage
 
   float4 vraw[NPX];
@@ -740,6 +751,8 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 #pragma unroll
     for (int c = 0; c < TC; ++c) acc[r][c] = 0.f;
 
+  long long seg_at = run_at;  // balanced mode: run position where the segment being accumulated starts
+  next_segment();
   if (kb_begin < nkb) {
     load_tile(kb_begin);
     store_tile(0);
@@ -749,9 +762,20 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   const int vcol = wp * 128 + 4 * lane;
   // broadcast from lane 0: tells the compiler the uniform operand's address is warp-uniform
   const int ucol = __shfl_sync(0xffffffffu, wq, 0) * TR;
-  for (int kb = kb_begin; kb < nkb; ++kb) {
-    const int buf = (kb - kb_begin) & 1;
-    if (kb + 1 < nkb) load_tile(kb + 1);
+  int buf = 0;
+  for (;;) {  // segments of this CTA's run (one pass unless the launch is balanced)
+  const int seg_end_kb = nkb;
+  const bool more = BALANCED && run_at < run_end;
+  for (int kb = kb_begin; kb < seg_end_kb; ++kb, buf ^= 1) {
+    const bool last = kb + 1 == seg_end_kb;
+    if (!last) {
+      load_tile(kb + 1);
+    } else if (more) {
+      // the next segment's first stage is fetched under this segment's last stage, so that no
+      // tile of the run starts with an exposed global-memory latency
+      next_segment();
+      load_tile(kb_begin);
+    }
     const uint32_t* vs = Vs + buf * BK * VS;
     const uint32_t* us = Us + buf * BK * US + ucol;
     // k rows 8..15 sit at the column with bit 3 flipped (see the staging above)
@@ -785,9 +809,20 @@ AMSIM_UNROLL_K
       AMSIM_K_HALVES(EXACT, LM)
     }
 #undef AMSIM_K_HALVES
-    if (kb + 1 < nkb) store_tile(buf ^ 1);
+    if (!last || more) store_tile(buf ^ 1);
     __syncthreads();
   }
+
+  // the tile just accumulated (the staging variables may already describe the next segment)
+  int cur_p, cur_q, cur_z, cur_kb0, cur_kb1;
+  if (BALANCED) {
+    decode_tile(seg_at, cur_p, cur_q, cur_z, cur_kb0, cur_kb1);
+    seg_at += cur_kb1 - cur_kb0;
+  } else {
+    cur_p = tile_p; cur_q = tile_q; cur_z = tile_z; cur_kb0 = kb_begin; cur_kb1 = nkb;
+  }
+  const int op0 = cur_p * BP, oq0 = cur_q * BQE;
+  float* __restrict__ Og = prm.O + (long long)cur_z * prm.o_bs;
 
   // ---- warps that shared a column group: add their register tiles in warp order ----------
   if (QS > 1) {
@@ -840,8 +875,8 @@ AMSIM_UNROLL_K
   // the workspace (slot 0: the run started inside the tile, slot 1: it started the tile) and
   // counts itself in; the CTA that completes the count adds all parked tiles of the tile in
   // CTA order (whoever it is, the order is the same) and writes the output.  Nobody waits.
-  if (BALANCED && (kb_begin != 0 || nkb != nkb_all)) {
-    float* slot = prm.ws + ((long long)blockIdx.x * 2 + (kb_begin == 0 ? 1 : 0)) * (TR * TC * NT);
+  if (BALANCED && (cur_kb0 != 0 || cur_kb1 != nkb_all)) {
+    float* slot = prm.ws + ((long long)blockIdx.x * 2 + (cur_kb0 == 0 ? 1 : 0)) * (TR * TC * NT);
 #pragma unroll
     for (int r = 0; r < TR; ++r)
 #pragma unroll
@@ -849,7 +884,7 @@ AMSIM_UNROLL_K
         if (AMSIM_IN(prm, BUF_WS, slot + (r * TC + c) * NT + t, float)) __stcg(slot + (r * TC + c) * NT + t, acc[r][c]);
     __threadfence();  // this thread's part of the tile is visible device-wide before the count
     __syncthreads();
-    const long long tile = ((long long)tile_z * prm.sk_ptiles + tile_p) * prm.sk_qtiles + tile_q;
+    const long long tile = ((long long)cur_z * prm.sk_ptiles + cur_p) * prm.sk_qtiles + cur_q;
     const long long first = tile * nkb_all, last = first + nkb_all;
     long long c0 = first * prm.sk_grid / prm.sk_iters;   // CTA whose run holds the tile's first block
     while (c0 > 0 && balanced_begin(c0, prm.sk_iters, prm.sk_grid) > first) --c0;
@@ -860,6 +895,8 @@ AMSIM_UNROLL_K
     if (t == 0) {
       const int arrived = AMSIM_IN(prm, BUF_WS, prm.sk_count + tile, int) ? atomicAdd(prm.sk_count + tile, 1) : 0;
       *flag_s = arrived == (int)(c1 - c0);  // c1 - c0 + 1 sharers
+      // the last sharer leaves the counter at zero for the next launch that uses this buffer
+      if (arrived == (int)(c1 - c0) && AMSIM_IN(prm, BUF_WS, prm.sk_count + tile, int)) prm.sk_count[tile] = 0;
     }
     __syncthreads();
     const bool completes = *flag_s != 0;
@@ -879,12 +916,17 @@ AMSIM_UNROLL_K
           for (int c = 0; c < TC; ++c)
             if (AMSIM_IN(prm, BUF_WS, src + (r * TC + c) * NT + t, float)) acc[r][c] = __fadd_rn(acc[r][c], __ldcg(src + (r * TC + c) * NT + t));
       }
-      store_out_tile(prm, acc, Og, p0 + vcol, q0 + ucol);
+      store_out_tile(prm, acc, Og, op0 + vcol, oq0 + ucol);
     }
   } else {
-    store_out_tile(prm, acc, Og, p0 + vcol, q0 + ucol);
+    store_out_tile(prm, acc, Og, op0 + vcol, oq0 + ucol);
   }
-  } while (BALANCED && run_at < run_end);
+  if (!more) break;
+#pragma unroll
+  for (int r = 0; r < TR; ++r)
+#pragma unroll
+    for (int c = 0; c < TC; ++c) acc[r][c] = 0.f;
+  }
 }
 
 // -----------------------------------------------------------------------------
