@@ -68,6 +68,7 @@ struct Switches {
   int no_additive = 0;      // AMSIM_NO_ADDITIVE=1       additive tables are looked up like any other (at lut_open)
   int wide = -1;            // AMSIM_WIDE=0/1            wide-tile filter gradient: never / whenever eligible
   int capture_cluster = -1; // AMSIM_CAPTURE_CLUSTER=0/1 small launches inside a graph capture: balanced / cluster split
+  int balanced_waves = -1;  // AMSIM_BALANCED_WAVES=n    CTAs of a balanced launch: n times the resident slots
   int bounds_shrink = 0;    // AMSIM_BOUNDS_SHRINK=n     bounds-checking build only: the output's recorded extent is n bytes
                             //                           short, so its last stores are caught (self-test of the checker)
 };
@@ -94,6 +95,7 @@ void load_switches() {
   flag("AMSIM_NO_ADDITIVE", w.no_additive);
   tri("AMSIM_WIDE", w.wide);
   tri("AMSIM_CAPTURE_CLUSTER", w.capture_cluster);
+  tri("AMSIM_BALANCED_WAVES", w.balanced_waves);
   tri("AMSIM_BOUNDS_SHRINK", w.bounds_shrink);
   g_sw = w;
 }
@@ -512,7 +514,9 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
     const long long iters = ctas * nkb;
     const long long waves = (ctas + slots - 1) / slots;
     const double fill = (double)ctas / (double)(waves * slots);
-    long long grid = slots;
+    // one CTA per resident slot; shorter runs in several waves measured slower (2 waves: +1.5 % on a
+    // ResNet-50 step, 6 waves: +4 %): every run parks up to two partial tiles
+    long long grid = (long long)slots * (sw().balanced_waves > 0 ? sw().balanced_waves : 1);
     // small problems are latency bound (a lone warp needs ~5 us per reduction block): spread them
     // down to 2 reduction blocks per CTA
     if (iters / grid < 2) grid = iters / 2;

@@ -46,6 +46,8 @@ class DataParallelSGD:
             self._close_bucket(cur)
         self._handles = []
         self._defer_allreduce = False   # while a step is being captured into a CUDA graph
+        self._expect = None             # per parameter: gradient reports per step (learned on the first step)
+        self._late = False
         # Gradient kernels of the AM layers write straight into the bucket memory (layers.GradSink):
         # no per-parameter accumulate kernel, and NCCL reduces the memory the kernels wrote.
         from .layers import GradSink
@@ -65,36 +67,73 @@ class DataParallelSGD:
         for p in params:
             p.grad = flat[off:off + p.numel()].view_as(p)
             off += p.numel()
-        self.buckets.append({"flat": flat, "params": params, "pending": len(params)})
+        self.buckets.append({"flat": flat, "params": params, "pending": len(params), "fired": {}, "launched": False})
 
     def _make_hook(self, bi):
-        def hook(_param):
+        def hook(param):
+            # Called when a gradient contribution of `param` is in place: by autograd after it
+            # accumulated one, and by an AM layer that wrote the gradient into the bucket itself
+            # (layers.GradSink).  A parameter may be reported several times per step: a shared
+            # parameter once per use, and a directly written one a second time by autograd, which
+            # fires its post-accumulate hook even for a gradient function that returned None
+            # (torch 2.11).  So the first step only counts the reports per parameter (its buckets
+            # are reduced after backward); from then on a parameter is complete at its last
+            # expected report, and a bucket is reduced when all its parameters are.
             b = self.buckets[bi]
-            b["pending"] -= 1
-            if b["pending"] == 0 and not self._defer_allreduce:
-                self._handles.append(dist.all_reduce(b["flat"], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            n = b["fired"].get(id(param), 0) + 1
+            b["fired"][id(param)] = n
+            if self._expect is None or self._defer_allreduce:
+                return
+            want = self._expect.get(id(param), 0)
+            if n == want:
+                b["pending"] -= 1
+                if b["pending"] == 0 and not b["launched"]:
+                    b["launched"] = True
+                    self._handles.append(dist.all_reduce(b["flat"], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            elif n > want and b["launched"]:
+                self._late = True   # a contribution after the bucket went out: the graph changed
         return hook
 
     def zero_grad(self):
         for b in self.buckets:
             b["flat"].zero_()
-            b["pending"] = len(b["params"])
+            b["fired"] = {}
+            b["launched"] = False
+            b["pending"] = (sum(1 for p in b["params"] if self._expect.get(id(p), 0) > 0)
+                            if self._expect is not None else len(b["params"]))
         for s in self._sinks:
             s.reset()
         self._handles = []
+        self._late = False
+
+    def _finish_allreduce(self):
+        """After backward: wait for the overlapped reductions, reduce the buckets that have not gone out
+        (first step; parameters that received no gradient), remember how often each parameter reports."""
+        for h in self._handles:
+            h.wait()
+        if self.world > 1:
+            if self._late:
+                raise RuntimeError("a parameter received a gradient contribution after its bucket had been "
+                                   "all-reduced: the autograd graph changed between steps")
+            for b in self.buckets:
+                if not b["launched"]:
+                    dist.all_reduce(b["flat"], op=dist.ReduceOp.SUM, group=self.group)
+                    b["launched"] = True
+            fired = {}
+            for b in self.buckets:
+                fired.update(b["fired"])
+            if self._expect is None or any(fired.get(k, 0) != v for k, v in self._expect.items()):
+                # first step, or a step that used the parameters differently: the next step starts
+                # from these counts (this one was reduced correctly: every late report raises above,
+                # and a bucket whose parameters reported less often than expected went out just now)
+                self._expect = {id(p): fired.get(id(p), 0) for p in self.params}
 
     def step(self, loss_fn: Callable[[], torch.Tensor]) -> torch.Tensor:
         """zero grads, ``loss = loss_fn()``, backward (all-reduce overlapped), SGD update."""
         self.zero_grad()
         loss = loss_fn()
         loss.backward()
-        for h in self._handles:
-            h.wait()
-        if self.world > 1:
-            # a parameter that received no gradient never fires its hook: reduce what is left
-            for b in self.buckets:
-                if b["pending"] != 0:
-                    dist.all_reduce(b["flat"], op=dist.ReduceOp.SUM, group=self.group)
+        self._finish_allreduce()
         self._update()
         return loss.detach()
 
