@@ -524,8 +524,9 @@ int launch_gather_t(cudaStream_t st, Params& p, int batch, int device) {
     // (one wave at 88 %: -7 %); with more waves the plain grid's tail is already short
     // with long reductions (shape A of the 3x3 microbenchmark: 3.5 waves of 36 blocks) it also pays on
     // larger grids (-2.5 %); with short ones (1x1 layers of 4-8 blocks) the parked partial tiles cost
-    // more than the tail (+3-4 %)
-    int mode = ((waves <= 2 && fill < 0.93) || (nkb >= 16 && fill < 0.95)) && grid >= 2 && nkb >= 2;
+    // more than the tail (+3-4 %), and so they do with an additive table, whose kernels run 1.5 times
+    // as fast (shape A: +6 %)
+    int mode = ((waves <= 2 && fill < 0.93) || (LM == LM_SMEM && nkb >= 16 && fill < 0.95)) && grid >= 2 && nkb >= 2;
     if (sw().balanced >= 0) mode = sw().balanced != 0 && grid >= 1;
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     CUDA_TRY(cudaStreamIsCapturing(st, &cap));
