@@ -198,18 +198,42 @@ def test_transformer_am_small_step_runs():
     assert np.isfinite(l1) and l1 < l0
 
 
-def test_cuda_graph_replay_matches_eager_steps():
-    """The whole train step (ops, split-K reduction, cluster launches, SGD update)
-    is capturable; replaying it gives the eager losses bit for bit."""
+class _ConvStack(torch.nn.Module):
+    """Three 3x3 AMConv2D layers and a dense head, sized so that their forward / input-gradient launches
+    share tiles between CTAs (balanced launches) inside a graph capture too."""
+
+    def __init__(self, lut):
+        super().__init__()
+        from approxtrain_b200.layers import AMConv2D, denseam
+        kw = dict(mant_mul_lut=lut, kernel_initializer="he_normal")
+        self.c1 = AMConv2D(8, 32, 3, padding="same", activation="relu", **kw)
+        self.c2 = AMConv2D(32, 64, 3, padding="same", activation="relu", **kw)
+        self.c3 = AMConv2D(64, 64, 3, padding="same", activation="relu", **kw)
+        self.f = denseam(64, 10, **kw)
+
+    def forward(self, x):
+        return self.f(self.c3(self.c2(self.c1(x))).mean((1, 2)))
+
+
+@pytest.mark.parametrize("which", ["lenet5", "conv_stack"])
+def test_cuda_graph_replay_matches_eager_steps(which):
+    """The whole train step (ops, split-K reduction, cluster and balanced launches, SGD update) is
+    capturable; replaying it gives the eager losses bit for bit.  In the capture the balanced launches
+    park their partial tiles in the persistent scratch, whose tile counters the kernel itself leaves at
+    zero for the next launch: a counter left dirty would show as a different (or missing) tile sum in
+    the second replay."""
     from approxtrain_b200.nets import LeNet5
     from approxtrain_b200.dp import DataParallelSGD
     g = torch.Generator().manual_seed(3)
-    x = torch.rand(64, 28, 28, 1, generator=g).cuda()
-    y = torch.randint(0, 10, (64,), generator=g).cuda()
+    if which == "lenet5":
+        x = torch.rand(64, 28, 28, 1, generator=g).cuda()
+    else:
+        x = torch.rand(16, 24, 24, 8, generator=g).cuda()
+    y = torch.randint(0, 10, (x.shape[0],), generator=g).cuda()
 
     def run(graphed):
         torch.manual_seed(1)
-        net = LeNet5(lut_path("MIT_7")).cuda()
+        net = (LeNet5(lut_path("MIT_7")) if which == "lenet5" else _ConvStack(lut_path("MBM_7"))).cuda()
         tr = DataParallelSGD(net, lr=0.05)
         fn = lambda: torch.nn.functional.cross_entropy(net(x), y)
         if not graphed:
