@@ -656,9 +656,17 @@ struct FgradPlan {
 // 128-row kernel.
 FgradPlan plan_fgrad(int P, int Q, int K, bool exact, int np, int sms);
 
-int pick_fgrad_rows(int P, int Q, int K, int sms, bool additive) {
+int pick_fgrad_rows(int P, int Q, int K, int sms, bool additive, bool vec) {
   if (sw().wide == 0) return 0;
   auto padded = [&](int bp) { return (double)(((long long)P + bp - 1) / bp) * bp; };
+  if (!vec) {
+    // no 128-bit gathers (channel count no multiple of 4): the 160-row tile with element-wise staging,
+    // where it has clearly less padded work than the 128-row tiles and the reduction is long
+    if (sw().wide < 0 && padded(160) > 0.85 * padded(128)) return 0;
+    const long long tiles5 = (((long long)P + 159) / 160) * (((long long)Q + BQ - 1) / BQ);
+    if (sw().wide < 0 && tiles5 * (((long long)K + BK - 1) / BK) < 8ll * 3 * sms) return 0;
+    return 5;
+  }
   int best = 8;
   double cost = padded(256);
   if (padded(288) <= cost) { best = 9; cost = padded(288); }
@@ -679,7 +687,7 @@ FgradPlan plan_fgrad(int P, int Q, int K, bool exact, int np, int sms) {
   FgradPlan f;
   f.np = exact ? 0 : np;
   const int bp = f.np ? 32 * f.np : 128;
-  const int slots = sms * (f.np ? 2 : AMSIM_CTAS1);  // resident CTAs on the whole GPU (launch bounds of the kernels)
+  const int slots = sms * (f.np >= 8 ? 2 : AMSIM_CTAS1);  // resident CTAs on the whole GPU (launch bounds of the kernels)
   const long long tiles = (((long long)P + bp - 1) / bp) * (((long long)Q + BQ - 1) / BQ);
   const long long chains = (long long)P * Q;
   f.thin = 0;
@@ -726,8 +734,10 @@ size_t fgrad_workspace(int P, int Q, int K, bool exact, int sms) {
   size_t need = plan_fgrad(P, Q, K, exact, 0, sms).ws_bytes;
   if (!exact) {
     for (int additive = 0; additive < 2; ++additive) {
-      const int np = pick_fgrad_rows(P, Q, K, sms, additive != 0);
-      if (np) need = std::max(need, plan_fgrad(P, Q, K, false, np, sms).ws_bytes);
+      for (int vec = 0; vec < 2; ++vec) {
+        const int np = pick_fgrad_rows(P, Q, K, sms, additive != 0, vec != 0);
+        if (np) need = std::max(need, plan_fgrad(P, Q, K, false, np, sms).ws_bytes);
+      }
     }
   }
   return need;
@@ -735,13 +745,14 @@ size_t fgrad_workspace(int P, int Q, int K, bool exact, int sms) {
 
 template <int LM, int NP>
 int launch_wide_fgrad_t(cudaStream_t st, Params& p, int device) {
+  constexpr bool VEC = NP != 5;
   p.tile_bytes = wide_tile_bytes(NP);
   const size_t smem = LM != LM_SMEM ? (size_t)p.tile_bytes + 16 : (size_t)p.tile_bytes + p.lut_align + p.lut_bytes;
-  int rc = ensure_smem(wide_fgrad<LM, NP>, smem, device);
+  int rc = ensure_smem(wide_fgrad<LM, NP, VEC>, smem, device);
   if (rc) return rc;
   dim3 grid((p.P + 32 * NP - 1) / (32 * NP), (p.Q + BQ - 1) / BQ, p.splits);
   AMSIM_COUNT_LAUNCH();
-  wide_fgrad<LM, NP><<<grid, WNT, smem, st>>>(p);
+  wide_fgrad<LM, NP, VEC><<<grid, WNT, smem, st>>>(p);
   CUDA_TRY(cudaGetLastError());
   if (p.splits > 1) {
     const long long n = (long long)p.P * p.Q;
@@ -824,8 +835,8 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   const int sms = sm_count(device);
   const bool vec = (p.g.SC % 4 == 0) && aligned16(p.V);
   FgradPlan f = plan_fgrad(p.P, p.Q, p.K, exact, 0, sms);
-  if (!exact && !f.thin && vec && (p.lut_mode == LM_SMEM || p.lut_mode == LM_ADD)) {
-    const int np = pick_fgrad_rows(p.P, p.Q, p.K, sms, p.lut_mode == LM_ADD);
+  if (!exact && !f.thin && (p.lut_mode == LM_SMEM || p.lut_mode == LM_ADD)) {
+    const int np = pick_fgrad_rows(p.P, p.Q, p.K, sms, p.lut_mode == LM_ADD, vec);
     if (np) f = plan_fgrad(p.P, p.Q, p.K, false, np, sms);
   }
   if (f.ws_bytes > 0) {
@@ -840,8 +851,12 @@ int launch_fgrad(cudaStream_t st, Params& p, bool exact, void* ws, size_t ws_byt
   if (f.np) {
     p.u_vec = aligned16(p.U) && p.u_sq == 1 && p.u_sk % 4 == 0 && p.Q % 4 == 0 && !sw().no_uvec;
     if (p.lut_mode == LM_ADD)
-      return f.np == 9 ? launch_wide_fgrad_t<LM_ADD, 9>(st, p, device) : launch_wide_fgrad_t<LM_ADD, 8>(st, p, device);
-    return f.np == 9 ? launch_wide_fgrad_t<LM_SMEM, 9>(st, p, device) : launch_wide_fgrad_t<LM_SMEM, 8>(st, p, device);
+      return f.np == 9   ? launch_wide_fgrad_t<LM_ADD, 9>(st, p, device)
+             : f.np == 8 ? launch_wide_fgrad_t<LM_ADD, 8>(st, p, device)
+                         : launch_wide_fgrad_t<LM_ADD, 5>(st, p, device);
+    return f.np == 9   ? launch_wide_fgrad_t<LM_SMEM, 9>(st, p, device)
+           : f.np == 8 ? launch_wide_fgrad_t<LM_SMEM, 8>(st, p, device)
+                       : launch_wide_fgrad_t<LM_SMEM, 5>(st, p, device);
   }
   if (f.thin) {
     {

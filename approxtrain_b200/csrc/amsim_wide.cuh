@@ -44,6 +44,10 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
   const int n = valid ? 16 : 0;  // 0 source bytes: the 16 bytes are zero-filled
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // One reduction step of a 16 (q) x 8 (p) register tile.
@@ -105,15 +109,20 @@ __device__ __forceinline__ void mac_wide(float (&acc)[TR][NP], const uint32_t (&
 // NP rows per lane: 8 (256-row tiles) or 9 (288-row tiles: the 9 taps of a 3x3
 // filter times a multiple of 32 channels tile without padding).  Lane l holds
 // rows 4l..4l+3 of every full group of 128 rows, then row l of a last group of 32.
+// NP = 5 with VEC = false (160-row tiles, 3 CTAs per SM, the lane operand staged
+// element by element with 4-byte cp.async): channel counts that are no multiple
+// of 4, whose rows would otherwise pad to the next multiple of 128 (a 7x7x3 first
+// layer: 147 rows fill 92 % of one 160-row tile, 57 % of two 128-row tiles).
 // -----------------------------------------------------------------------------
 template <int NP>
 __device__ __forceinline__ int wide_fgrad_row(int lane, int c) {
   return c < (NP / 4) * 4 ? (c >> 2) * 128 + 4 * lane + (c & 3) : (NP / 4) * 128 + (NP % 4) * lane + (c & 3);
 }
 
-template <int LM, int NP>
-__global__ void __launch_bounds__(WNT, 2) wide_fgrad(const Params prm) {
-  static_assert(NP == 8 || NP == 9, "rows per lane");
+template <int LM, int NP, bool VEC = true>
+__global__ void __launch_bounds__(WNT, NP >= 8 ? 2 : 3) wide_fgrad(const Params prm) {
+  static_assert(NP == 5 || NP == 8 || NP == 9, "rows per lane");
+  static_assert(VEC == (NP != 5), "element-wise staging is written for the 128 + 32 columns of the 160-row tile");
   constexpr int NU = BK * BQ / WNT;
   constexpr int BPT = 32 * NP;            // rows of the CTA tile
   constexpr int FS = wide_fgrad_pitch(NP);
@@ -140,7 +149,44 @@ __global__ void __launch_bounds__(WNT, 2) wide_fgrad(const Params prm) {
 
   // 16-byte group c = t + 128 i (i < NP) of the BK x GPR groups of a stage: k row c / GPR, rows
   // 4 (c % GPR) .. + 3 (one tap: the channel count is a multiple of 4)
+  // Element-wise staging (VEC false): thread t fills column t of every k row and column 128 + lane
+  // of k rows 4 (t / 32) .. + 3; the columns' taps are decoded once.
+  int e_kh[2] = {0, 0}, e_kw[2] = {0, 0}, e_ch[2] = {0, 0};
+  bool e_ok[2] = {false, false};
+  if (!VEC) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t pg = (uint32_t)(p0 + (j == 0 ? t : 128 + lane));
+      const uint32_t tap = fdiv(pg, g.d_sc);
+      e_ch[j] = (int)(pg - tap * (uint32_t)g.SC);
+      e_kh[j] = (int)fdiv(tap, g.d_kw);
+      e_kw[j] = (int)tap - e_kh[j] * g.KW;
+      e_ok[j] = pg < (uint32_t)prm.P;
+    }
+  }
   auto issue_v = [&](int kb, int buf) {
+    if (!VEC) {
+#pragma unroll 4
+      for (int kr = 0; kr < BK; ++kr) {
+        const int pix = kbeg + kb * BK + kr;
+        const uint32_t n = fdiv((uint32_t)pix, g.d_img);
+        const uint32_t rem = (uint32_t)pix - n * (uint32_t)(g.PH * g.PW);
+        const uint32_t a = fdiv(rem, g.d_pw);
+        const uint32_t b = rem - a * (uint32_t)g.PW;
+        const int u0 = (int)a * g.ps_h - g.off_t, v0 = (int)b * g.ps_w - g.off_l;
+        const float* img = Vg + (long long)n * ((long long)g.SH * g.SW * g.SC);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          if (j == 1 && (kr >> 2) != (t >> 5)) continue;
+          const int u = u0 + e_kh[j], v = v0 + e_kw[j];
+          bool ok = e_ok[j] && pix < kend && (unsigned)u < (unsigned)g.lim_h && (unsigned)v < (unsigned)g.lim_w;
+          const float* src = ok ? img + ((long long)(u * g.SW + v) * g.SC + e_ch[j]) : Vg;
+          ok = ok && AMSIM_IN(prm, BUF_V, src, float);
+          cp_async4(smem_base + (uint32_t)(((buf * BK + kr) * FS + (j == 0 ? t : 128 + lane)) * 4), src, ok);
+        }
+      }
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < NP; ++i) {
       const int c = t + WNT * i;
@@ -230,10 +276,12 @@ __global__ void __launch_bounds__(WNT, 2) wide_fgrad(const Params prm) {
     for (int kk = 0; kk < BK; ++kk) {
       uint32_t wv[NP];
       const uint4 lo = *reinterpret_cast<const uint4*>(vs + kk * FS + 4 * lane);
-      const uint4 hi = *reinterpret_cast<const uint4*>(vs + kk * FS + 128 + 4 * lane);
       wv[0] = lo.x; wv[1] = lo.y; wv[2] = lo.z; wv[3] = lo.w;
-      wv[4] = hi.x; wv[5] = hi.y; wv[6] = hi.z; wv[7] = hi.w;
-      if (NP == 9) wv[NP - 1] = vs[kk * FS + 256 + lane];
+      if (NP >= 8) {
+        const uint4 hi = *reinterpret_cast<const uint4*>(vs + kk * FS + 128 + 4 * lane);
+        wv[4] = hi.x; wv[5] = hi.y; wv[6] = hi.z; wv[7] = hi.w;
+      }
+      if (NP % 4 == 1) wv[NP - 1] = vs[kk * FS + (NP / 4) * 128 + lane];
       mac_wide<LM, NP>(acc, wv, us + kk * US, lut_base, sh, prm.cmask, prm.mult, keep);
     }
     if (kb + 1 < nkb) store_u_tile(buf ^ 1);

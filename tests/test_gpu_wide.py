@@ -114,3 +114,38 @@ def test_wide_dense_weight_gradient(ops, oracle, luts, monkeypatch):
         dx, dw = ops.denseam_grad(dev(gy), dev(x), dev(w), lp)
         close(dx.cpu().numpy(), oracle.dense_bwd_input(w, gy, lut, m), "wide dense input-grad")
         close(dw.cpu().numpy(), oracle.dense_bwd_weight(x, gy, lut, m), "wide dense weight-grad")
+
+
+# (n, h, w, c, kh, kw, k, stride, padding): channel counts that are NO multiple of 4 take the 160-row tile
+# with element-wise staging (by default only for long reductions such as a 7x7x3 first layer)
+TALL5_CONV = [
+    (2, 30, 30, 3, 7, 7, 64, 2, "VALID"),    # the first layer of a ResNet: 147 rows in one 160-row tile
+    (2, 12, 11, 6, 5, 5, 16, 1, "VALID"),    # LeNet-5's second convolution: 150 rows, 16 columns
+    (3, 9, 9, 5, 3, 3, 70, 1, "SAME"),       # 45 rows of one tile, padding taps, ragged columns
+    (1, 14, 14, 30, 3, 3, 33, 2, "SAME"),    # 270 rows: two tiles, the second ragged; stride 2
+    (2, 10, 10, 1, 5, 5, 6, 1, "SAME"),      # one input channel
+]
+
+
+@pytest.mark.parametrize("lname", ["MBM_7", "MIT_7"])
+@pytest.mark.parametrize("case", TALL5_CONV)
+def test_filter_gradient_on_the_160_row_tile(ops, oracle, luts, monkeypatch, case, lname):
+    n, h, w, c, kh, kw, k, s, pad = case
+    lut, m = luts[lname]
+    rng = np.random.default_rng(zlib.crc32(repr((case, lname)).encode()))
+    x = rng.standard_normal((n, h, w, c)).astype(np.float32)
+    x[x < -0.8] = 0.0
+    g = oracle.geometry(n, h, w, c, kh, kw, k, s, s, pad)
+    dy = rng.standard_normal((n, g.out_h, g.out_w, k)).astype(np.float32)
+    dy[dy < -1.0] = 0.0
+    want = oracle.conv2d_bwd_filter(g, x, dy, lut, m)
+    kw_ = dict(strides=[1, s, s, 1], padding=pad, mant_mul_lut=lut_path(lname))
+    got = {}
+    for sw in ("0", "1"):
+        set_switch(monkeypatch, "AMSIM_WIDE", sw)
+        got[sw] = ops.convam_filter_grad((kh, kw, c, k), dev(x), dev(dy), **kw_).cpu().numpy()
+        close(got[sw], want, f"filter-grad AMSIM_WIDE={sw}")
+    # an input tensor that is not 16-byte aligned takes the same tile (4-byte copies need no more)
+    xo = torch.empty(x.size + 1, dtype=torch.float32, device="cuda")[1:].view(x.shape)
+    xo.copy_(dev(x))
+    close(ops.convam_filter_grad((kh, kw, c, k), xo, dev(dy), **kw_).cpu().numpy(), want, "filter-grad, unaligned input")
