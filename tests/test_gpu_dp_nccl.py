@@ -2,7 +2,10 @@
 two ranks must give the update of the full batch on one GPU, within the FP32
 reduction-order tolerance, for the networks without batch statistics: LeNet-300-100
 (denseam layers) and LeNet-5 (AMConv2D filter gradients cross the all-reduce too).
-Skipped where fewer than two GPUs are visible."""
+The NCCL cases are skipped where fewer than two GPUs are visible; the same check also
+runs with both ranks on ONE GPU over gloo (the ranks' kernels never wait on one another:
+the exchange is a host-side collective), so a single-GPU box covers the trainer with the
+real AM kernels too."""
 import os
 import socket
 
@@ -38,13 +41,13 @@ def _net(which, dev):
     return LeNet5(lut_path("MIT_7")).to(dev)
 
 
-def _worker(rank, world, port, out, which, graph=False):
+def _worker(rank, world, port, out, which, graph=False, one_gpu=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world)
+    torch.cuda.set_device(0 if one_gpu else rank)
+    dist.init_process_group("gloo" if one_gpu else "nccl", rank=rank, world_size=world)
     from approxtrain_b200.dp import DataParallelSGD
-    dev = torch.device("cuda", rank)
+    dev = torch.device("cuda", 0 if one_gpu else rank)
     net = _net(which, dev)
     tr = DataParallelSGD(net, lr=0.05)
     x, y = _data(which)
@@ -69,7 +72,16 @@ def _worker(rank, world, port, out, which, graph=False):
 def test_two_gpus_give_the_full_batch_update(tmp_path, which, graph):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), which, graph), nprocs=2, join=True)
+    _check(tmp_path, which, graph, one_gpu=False)
+
+
+@pytest.mark.parametrize("which,graph", [("lenet300100", False), ("lenet5", False), ("lenet5", True)])
+def test_two_ranks_on_one_gpu_give_the_full_batch_update(tmp_path, which, graph):
+    _check(tmp_path, which, graph, one_gpu=True)
+
+
+def _check(tmp_path, which, graph, one_gpu):
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), which, graph, one_gpu), nprocs=2, join=True)
     r0 = torch.load(tmp_path / "rank0.pt")
     r1 = torch.load(tmp_path / "rank1.pt")
     for a, b in zip(r0, r1):
@@ -87,5 +99,5 @@ def test_two_gpus_give_the_full_batch_update(tmp_path, which, graph):
     for a, p in zip(r0, net.parameters()):
         worst = max(worst, float((a - p.detach().cpu()).abs().max()))
         assert torch.allclose(a, p.detach().cpu(), atol=1e-6, rtol=1e-4)
-    print(f"{which}{' (CUDA graphs)' if graph else ''}: replicas identical on 2 GPUs; "
+    print(f"{which}{' (CUDA graphs)' if graph else ''}: replicas identical on {'one GPU, 2 gloo ranks' if one_gpu else '2 GPUs'}; "
           f"max |sharded - full batch| over all parameters {worst:.3e}")
