@@ -310,3 +310,20 @@ def test_bench_prints_one_complete_line_for_a_small_workload():
         assert key in d, key
     assert d["value"] > 0 and d["gpu_launches"] > 0 and d["e2e"]["value"] > 0 and d["e2e"]["h2d_bytes_per_step"] > 0
     assert d["am_ops"]["layers"] and d["roofline"]["frac"] > 0
+
+
+def test_bench_single_layer_workload():
+    """bench.py --workload layer: one AMConv2D layer's three ops timed in isolation, one JSON line."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--workload", "layer", "--shape", "4,14,14,32,3,3,64,1,SAME",
+                          "--steps", "2", "--warmup", "3"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-3000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert [k["op"] for k in d["kernels"]] == ["fwd", "input_grad", "filter_grad"]
+    assert d["value"] > 0 and all(k["ms"] > 0 and k["frac_of_roofline"] > 0 for k in d["kernels"])
