@@ -21,6 +21,8 @@ reference-order mode (``AMSIM_DETERMINISTIC``).
 """
 from __future__ import annotations
 
+import contextlib
+
 import ctypes as C
 import threading
 from typing import Sequence
@@ -348,9 +350,11 @@ def denseam(input: torch.Tensor, weights: torch.Tensor, mant_mul_lut: str = "",
 
 
 def denseam_grad(grad: torch.Tensor, input: torch.Tensor, weights: torch.Tensor, mant_mul_lut: str = "",
-                 deterministic: bool = False, out_weights: torch.Tensor = None):
+                 deterministic: bool = False, out_weights: torch.Tensor = None, weights_stream=None):
     """Returns (grad_input, grad_weights) like DenseamGrad (denseam.cc:177-235).  ``out_weights``
-    (optional): write grad_weights into this tensor instead of a new one."""
+    (optional): write grad_weights into this tensor instead of a new one.  ``weights_stream`` (optional
+    ``torch.cuda.Stream`` that already waits for the operands): the weight gradient and its scratch are
+    launched there, the input gradient on the current stream; the caller joins the two."""
     g, x, w = _prep(grad, "grad"), _prep(input, "input"), _prep(weights, "weights")
     b, kin = x.shape
     u = w.shape[1]
@@ -359,13 +363,17 @@ def denseam_grad(grad: torch.Tensor, input: torch.Tensor, weights: torch.Tensor,
     lut = get_lut(mant_mul_lut, x.device)
     fl = _flags(deterministic) | _dtype_flag(g, x, w)
     dx = torch.empty_like(x)
-    dw = _out_tensor(out_weights, tuple(w.shape), w.dtype, w.device, "denseam_grad")
     ws_bytes = lib.amsim_dense_bwd_weight_workspace(b, u, kin, fl)
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
     with torch.cuda.device(x.device):
-        check(lib.amsim_dense_bwd_weight(_stream(), lut.handle, _ptr(x), _ptr(g), _ptr(dw), b, u, kin,
-                                         _ptr(ws) if ws is not None else None, ws_bytes, fl))
-        check(lib.amsim_dense_bwd_input(_stream(), lut.handle, _ptr(w), _ptr(g), _ptr(dx), b, u, kin, fl))
+        if weights_stream is not None:   # input gradient first: it is the one the rest of backward waits for
+            check(lib.amsim_dense_bwd_input(_stream(), lut.handle, _ptr(w), _ptr(g), _ptr(dx), b, u, kin, fl))
+        with (torch.cuda.stream(weights_stream) if weights_stream is not None else contextlib.nullcontext()):
+            dw = _out_tensor(out_weights, tuple(w.shape), w.dtype, w.device, "denseam_grad")
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes else None
+            check(lib.amsim_dense_bwd_weight(_stream(), lut.handle, _ptr(x), _ptr(g), _ptr(dw), b, u, kin,
+                                             _ptr(ws) if ws is not None else None, ws_bytes, fl))
+        if weights_stream is None:
+            check(lib.amsim_dense_bwd_input(_stream(), lut.handle, _ptr(w), _ptr(g), _ptr(dx), b, u, kin, fl))
     return dx, dw
 
 

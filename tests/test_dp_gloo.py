@@ -98,7 +98,7 @@ def _install_cpu_ops():
             y = y + b
         return torch.relu(y) if activation == "relu" else y
 
-    def denseam_grad(g, x, w, lut="", deterministic=False, out_weights=None):
+    def denseam_grad(g, x, w, lut="", deterministic=False, out_weights=None, weights_stream=None):
         dw = x.t() @ g
         if out_weights is not None:
             out_weights.copy_(dw)
