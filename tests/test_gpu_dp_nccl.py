@@ -41,7 +41,7 @@ def _net(which, dev):
     return LeNet5(lut_path("MIT_7")).to(dev)
 
 
-def _worker(rank, world, port, out, which, graph=False, one_gpu=False):
+def _worker(rank, world, port, out, which, graph=False, one_gpu=False, bucket_bytes=32 << 20):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(0 if one_gpu else rank)
@@ -49,7 +49,7 @@ def _worker(rank, world, port, out, which, graph=False, one_gpu=False):
     from approxtrain_b200.dp import DataParallelSGD
     dev = torch.device("cuda", 0 if one_gpu else rank)
     net = _net(which, dev)
-    tr = DataParallelSGD(net, lr=0.05)
+    tr = DataParallelSGD(net, lr=0.05, bucket_bytes=bucket_bytes)
     x, y = _data(which)
     n = x.shape[0] // world
     xs, ys = x[rank * n:(rank + 1) * n].to(dev), y[rank * n:(rank + 1) * n].to(dev)
@@ -68,20 +68,27 @@ def _worker(rank, world, port, out, which, graph=False, one_gpu=False):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("which,graph", [("lenet300100", False), ("lenet5", False), ("lenet5", True)])
-def test_two_gpus_give_the_full_batch_update(tmp_path, which, graph):
+# (network, replay from CUDA graphs, bucket size): the small buckets split LeNet-5's ten parameters over
+# several all-reduces that start while backward is still running on both of the layers' streams
+CASES = [("lenet300100", False, 32 << 20), ("lenet5", False, 32 << 20), ("lenet5", True, 32 << 20), ("lenet5", False, 4096),
+         ("lenet300100", False, 100000)]
+IDS = ["lenet300100", "lenet5", "lenet5-graphs", "lenet5-small-buckets", "lenet300100-small-buckets"]
+
+
+@pytest.mark.parametrize("which,graph,bucket_bytes", CASES, ids=IDS)
+def test_two_gpus_give_the_full_batch_update(tmp_path, which, graph, bucket_bytes):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    _check(tmp_path, which, graph, one_gpu=False)
+    _check(tmp_path, which, graph, False, bucket_bytes)
 
 
-@pytest.mark.parametrize("which,graph", [("lenet300100", False), ("lenet5", False), ("lenet5", True)])
-def test_two_ranks_on_one_gpu_give_the_full_batch_update(tmp_path, which, graph):
-    _check(tmp_path, which, graph, one_gpu=True)
+@pytest.mark.parametrize("which,graph,bucket_bytes", CASES, ids=IDS)
+def test_two_ranks_on_one_gpu_give_the_full_batch_update(tmp_path, which, graph, bucket_bytes):
+    _check(tmp_path, which, graph, True, bucket_bytes)
 
 
-def _check(tmp_path, which, graph, one_gpu):
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), which, graph, one_gpu), nprocs=2, join=True)
+def _check(tmp_path, which, graph, one_gpu, bucket_bytes):
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), which, graph, one_gpu, bucket_bytes), nprocs=2, join=True)
     r0 = torch.load(tmp_path / "rank0.pt")
     r1 = torch.load(tmp_path / "rank1.pt")
     for a, b in zip(r0, r1):
