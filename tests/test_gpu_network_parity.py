@@ -37,6 +37,9 @@ class Recorder:
 
             def wrapped(*a, __orig=orig, __name=name, **k):
                 out = __orig(*a, **k)
+                # a layer may have launched part of the op on its second stream (the weight gradient of
+                # denseam_grad) and joins after the call returns: wait for the whole device before copying
+                torch.cuda.synchronize()
                 keep = lambda v: v.detach().cpu().numpy().copy() if isinstance(v, torch.Tensor) else v
                 outs = tuple(keep(o) for o in out) if isinstance(out, tuple) else keep(out)
                 self.calls.append((__name, tuple(keep(v) for v in a), {kk: keep(v) for kk, v in k.items() if kk not in ("out", "out_weights")}, outs))
