@@ -327,3 +327,30 @@ def test_bench_single_layer_workload():
     d = json.loads(lines[0])
     assert [k["op"] for k in d["kernels"]] == ["fwd", "input_grad", "filter_grad"]
     assert d["value"] > 0 and all(k["ms"] > 0 and k["frac_of_roofline"] > 0 for k in d["kernels"])
+
+
+def test_second_backward_stream_changes_no_bit():
+    """A layer's parameter gradients run on a second stream beside its input gradient; with the switch off
+    everything runs in order on one stream.  Same kernels, same operands: the parameters after three steps
+    are bit-identical either way (a missing join between the streams would show here as a difference)."""
+    from approxtrain_b200 import layers
+    from approxtrain_b200.dp import DataParallelSGD
+    g = torch.Generator().manual_seed(5)
+    x = torch.rand(16, 24, 24, 8, generator=g).cuda()
+    y = torch.randint(0, 10, (16,), generator=g).cuda()
+
+    def run(two_streams):
+        keep, layers.TWO_STREAM_BACKWARD = layers.TWO_STREAM_BACKWARD, two_streams
+        try:
+            torch.manual_seed(1)
+            net = _ConvStack(lut_path("MBM_7")).cuda()
+            tr = DataParallelSGD(net, lr=0.05)
+            for _ in range(3):
+                tr.step(lambda: torch.nn.functional.cross_entropy(net(x), y))
+            torch.cuda.synchronize()
+            return [p.detach().cpu() for p in net.parameters()]
+        finally:
+            layers.TWO_STREAM_BACKWARD = keep
+
+    for a, b in zip(run(True), run(False)):
+        assert torch.equal(a, b)
