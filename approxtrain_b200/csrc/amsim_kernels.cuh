@@ -526,8 +526,6 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
   const Gather& g = prm.g;
   const int nkb_all = (prm.K + BK - 1) / BK;
 
-  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
-
   uint32_t* flag_s = Fs;  // balanced mode (fast kernels only, where Fs is otherwise unused): "this CTA completes the tile"
   // Balanced mode: this CTA's run of (tile, reduction block) pairs; otherwise one pass.
   long long run_at = 0, run_end = 0;
@@ -753,10 +751,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) gather_ge
 
   long long seg_at = run_at;  // balanced mode: run position where the segment being accumulated starts
   next_segment();
-  if (kb_begin < nkb) {
-    load_tile(kb_begin);
-    store_tile(0);
-  }
+  if (kb_begin < nkb) load_tile(kb_begin);
+  // the table is copied while the first stage's global loads are in flight
+  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+  if (kb_begin < nkb) store_tile(0);
   __syncthreads();
 
   const int vcol = wp * 128 + 4 * lane;
@@ -963,7 +961,6 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
   const float* __restrict__ Vg = prm.V;
   const float* __restrict__ Ug = prm.U;
 
-  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
 
   // ---- this thread's 4 consecutive p (same for every k row it stages) ---------
   const int pl = 4 * (t % GPR);
@@ -1085,10 +1082,10 @@ __global__ void __launch_bounds__(WP * 128, WP == 1 ? AMSIM_CTAS1 : 2) fgrad_gem
   const int nkb = (kend - kbeg + BK - 1) / BK;
   const int vcol = wp * 128 + 4 * lane;
   const int ucol = wq * TR;
-  if (nkb > 0) {
-    load_tile(0);
-    store_tile(0);
-  }
+  if (nkb > 0) load_tile(0);
+  // the table is copied while the first stage's global loads are in flight
+  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, NT);
+  if (nkb > 0) store_tile(0);
   __syncthreads();
   for (int kb = 0; kb < nkb; ++kb) {
     const int buf = kb & 1;

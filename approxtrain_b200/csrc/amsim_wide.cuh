@@ -145,7 +145,6 @@ __global__ void __launch_bounds__(WNT, NP >= 8 ? 2 : 3) wide_fgrad(const Params 
   const int sh = 23 - prm.m;
   const uint32_t keep = ~((1u << sh) - 1u);
 
-  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, WNT);
 
   // 16-byte group c = t + 128 i (i < NP) of the BK x GPR groups of a stage: k row c / GPR, rows
   // 4 (c % GPR) .. + 3 (one tap: the channel count is a multiple of 4)
@@ -260,8 +259,10 @@ __global__ void __launch_bounds__(WNT, NP >= 8 ? 2 : 3) wide_fgrad(const Params 
   if (nkb > 0) {
     issue_v(0, 0);
     load_u(0);
-    store_u_tile(0);
   }
+  // the table is copied while the first stage's copies and loads are in flight
+  if (LM == LM_SMEM) copy_lut_to_smem(lut_s, prm.lut, prm.lut_bytes, t, WNT);
+  if (nkb > 0) store_u_tile(0);
   cp_async_wait_all();
   __syncthreads();
   for (int kb = 0; kb < nkb; ++kb) {
