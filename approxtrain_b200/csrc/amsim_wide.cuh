@@ -24,7 +24,8 @@
 // 16 x 4 kernels.  Products of one step are issued in groups of four rows so
 // that only four "operand is zero" predicates are live at a time.
 //
-// Fast mode, 128-bit gathers and tables in shared memory (or additive) only.
+// Fast mode and tables in shared memory (or additive) only; 128-bit gathers, except for
+// the 160-row variant (5 rows per lane), which stages element by element.
 // A gather-side kernel of the same shape (forward / input gradient) was built
 // in two layouts and measured 4-14 % slower than the 16 x 4 gather_gemm on the
 // 3x3 microbenchmark shapes; it is not kept.
